@@ -5,7 +5,9 @@ from .specs import (  # noqa: F401
     ScalarRMSNormSpec, SinusoidEmbeddingSpec, DenseMLPSpec, GatedRecurrenceSpec, TalkingAttentionSpec, PostNormBlockSpec,
     NormedEmbeddingSpec, StreamInjectSpec, RetentionSpec, TimeMixSpec, GatedUnitSpec, RotaryValueAttentionSpec,
     ParallelMixerSpec, RoutedExpertsSpec, TokenSideSpec, SandwichBlockSpec,
+    PagedStream, PagedCacheNeed, GroupRMSNormSpec, CausalConvSpec, LatentAttentionSpec, DepthAverageBlockSpec,
 )
 from .qwen3 import Qwen3Config  # noqa: F401
 from .kafunex import KafunexConfig  # noqa: F401
 from .lunelorn import LunelornConfig  # noqa: F401
+from .filorax import FiloraxConfig  # noqa: F401

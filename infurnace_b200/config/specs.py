@@ -580,15 +580,27 @@ class ParallelMixerSpec:
 
 @dataclass(frozen=True)
 class RoutedExpertsSpec:
-    """A mixture of gated feed-forwards without biases.  Router logits z = R h in 32-bit; each token runs the
-    ``top`` experts with the largest logits, weighted by the softmax over those logits only; an expert is
-    down(act(gate h) * (up h)).  ``experts`` names each expert's (gate, up, down) tensors."""
+    """A mixture of gated feed-forwards without biases.  Router logits z = R h in 32-bit; an expert is
+    down(act(gate h) * (up h)).  ``experts`` names each expert's (gate, up, down) tensors.
+
+    ``scoring`` "chosen" (the default): each token runs the ``top`` experts with the largest logits, weighted by the
+    softmax over those logits only.  ``scoring`` "all": the scores are the softmax over all experts, the ``top`` largest
+    scores are chosen and the weights are those scores times ``weight_scale``, not renormalised.  ``groups`` =
+    (count, keep): the experts form ``count`` equal groups of neighbours, a group's score is its largest score, and only
+    experts of the ``keep`` best groups can be chosen (None: no such limit).  ``shared``: a gated feed-forward that
+    every token runs, added to the sum; with ``shared_gate`` (a tensor [1, hidden]) it is first multiplied by
+    sigmoid(shared_gate . h), one number per token."""
     hidden_size: int
     intermediate_size: int
     top: int
     activation: str
     router: str
     experts: Tuple[Tuple[str, str, str], ...]
+    scoring: str = "chosen"
+    weight_scale: float = 1.0
+    groups: Optional[Tuple[int, int]] = None
+    shared: Optional[GatedMLPSpec] = None
+    shared_gate: Optional[str] = None
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         t = {self.router: TensorSpec((len(self.experts), self.hidden_size), init=(0.0, 0.3))}
@@ -596,6 +608,10 @@ class RoutedExpertsSpec:
             t[gate] = TensorSpec((self.intermediate_size, self.hidden_size))
             t[up] = TensorSpec((self.intermediate_size, self.hidden_size))
             t[down] = TensorSpec((self.hidden_size, self.intermediate_size))
+        if self.shared is not None:
+            t.update(self.shared.tensors())
+        if self.shared_gate is not None:
+            t[self.shared_gate] = TensorSpec((1, self.hidden_size), init=(0.0, 0.1))
         return t
 
     def cache_need(self):
@@ -648,6 +664,122 @@ class SandwichBlockSpec:
 
     def cache_need(self):
         return self.mixer.cache_need()
+
+
+# --------------------------------------------------------------------------- parts of latent-attention decoders
+@dataclass(frozen=True)
+class GroupRMSNormSpec:
+    """RMS norm in groups: the row is split into ``groups`` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps); the whole row is then multiplied by ``weight``.  One group is the plain RMS norm."""
+    size: int
+    eps: float
+    groups: int
+    weight: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.weight: TensorSpec((self.size,))}
+
+
+@dataclass(frozen=True)
+class CausalConvSpec:
+    """A short causal convolution over time on each channel, added to its input:
+    y_t = h_t + sum_j w[:, j] * h_(t - taps + 1 + j), zeros before the sequence's start; ``weight`` [width, taps], no
+    bias.  The last taps - 1 inputs of a sequence are its state."""
+    width: int
+    taps: int
+    weight: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.weight: TensorSpec((self.width, self.taps), init=(0.0, 0.2))}
+
+    def cache_need(self):
+        return StateNeed((max(self.taps - 1, 1), self.width))
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are made from a small latent per token, which is all that is cached.
+
+    q = Q h, laid out head by head as [head_dim unrotated, rot_dim rotated].  D h has kv_rank + rot_dim rows: the first
+    kv_rank, RMS-normalised with ``latent_norm`` (a plain weight), are the latent c; the last rot_dim are one rotated key
+    part shared by all heads.  Per head k = UK c and v = UV c; score = (q_unrotated . k + q_rotated . k_rotated) * scale.
+    ``position`` (a :class:`RotarySpec` over the rot_dim part) turns the rotated parts of q and of the key by the token's
+    position.  ``window`` w: position i sees j with 0 <= i - j < w (None: every j <= i).  ``sink``: a tensor [heads]; exp
+    of it joins the softmax's denominator, with no key and no value.  ``gate``: the heads side by side are multiplied by
+    sigmoid(G h) before ``o_proj``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    value_head_dim: int
+    kv_rank: int
+    scale: float
+    eps: float
+    q_proj: str
+    down_proj: str
+    latent_norm: str
+    k_up: str
+    v_up: str
+    o_proj: str
+    position: Optional[RotarySpec] = None
+    window: Optional[int] = None
+    sink: Optional[str] = None
+    gate: Optional[str] = None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        W, H = self.hidden_size, self.num_heads
+        t = {self.q_proj: TensorSpec((H * (self.head_dim + self.rot_dim), W)),
+             self.down_proj: TensorSpec((self.kv_rank + self.rot_dim, W)),
+             self.latent_norm: TensorSpec((self.kv_rank,)),
+             self.k_up: TensorSpec((H * self.head_dim, self.kv_rank)),
+             self.v_up: TensorSpec((H * self.value_head_dim, self.kv_rank)),
+             self.o_proj: TensorSpec((W, H * self.value_head_dim))}
+        if self.sink is not None:
+            t[self.sink] = TensorSpec((H,), init=(0.0, 1.0))
+        if self.gate is not None:
+            t[self.gate] = TensorSpec((H * self.value_head_dim, W))
+        return t
+
+    def cache_need(self):
+        streams = (PagedStream("latent", 1, self.kv_rank),)
+        if self.rot_dim:
+            streams += (PagedStream("rotated_key", 1, self.rot_dim),)
+        return PagedCacheNeed(streams, self.window)
+
+
+@dataclass(frozen=True)
+class DepthAverageBlockSpec:
+    """A pre-norm block with a residual multiplier, an input convolution before each sublayer and a weighted average
+    over depth.  x += mult * mixer(conv1(norm1(x))); x += mult * ffn(conv2(norm2(x))) (``ffn`` None: no feed-forward).
+    With X_0 the embedding's output and X_(d) the result of the block at depth d - 1 before averaging, the block at
+    depth ``depth`` hands on sum_j ``average``[j] * X_j, j = 0 .. depth + 1 (``average`` None: no averaging).  ``depths`` is
+    the number of such blocks in the model: a step keeps depths + 1 rows per token.  ``mixer_conv`` / ``ffn_conv`` may be
+    None."""
+    hidden_size: int
+    depth: int
+    depths: int
+    residual_mult: float
+    mixer_norm: object
+    mixer: object
+    mixer_conv: Optional[CausalConvSpec] = None
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    ffn_conv: Optional[CausalConvSpec] = None
+    average: Optional[str] = None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        t = {}
+        for part in (self.mixer_norm, self.mixer, self.mixer_conv, self.ffn_norm, self.ffn, self.ffn_conv):
+            if part is not None:
+                t.update(part.tensors())
+        if self.average is not None:
+            t[self.average] = TensorSpec((self.depth + 2,), init=(1.0 / (self.depth + 2), 0.1))
+        return t
+
+    def cache_need(self):
+        """Entry 0: the mixer's; entries 1 and 2: the states of the two convolutions (None where there is none)."""
+        return (self.mixer.cache_need(), self.mixer_conv.cache_need() if self.mixer_conv is not None else None,
+                self.ffn_conv.cache_need() if self.ffn_conv is not None and self.ffn is not None else None)
 
 
 # --------------------------------------------------------------------------- the order

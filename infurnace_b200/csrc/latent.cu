@@ -1,0 +1,303 @@
+// Row-wise steps of decoders whose attention keeps a small latent per token: the RMS norm in groups (with the residual
+// addition and a residual multiplier folded in), the short causal convolution in front of a sublayer (its last inputs
+// are state of a sequence), the weighted average over depth (with the next norm folded in), the preparation of queries
+// and latents for the latent attention, and the output gate.  Statistics, sums, angles and the stream are float32.
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------
+// The norm in groups of a row that lies in shared memory: out[e] = row[e] * rsqrt(mean over e's group of row^2 + eps) * w[e].
+// Every thread of the block calls it; `scratch` holds 33 floats.
+// ------------------------------------------------------------------------------------------
+template <typename TO>
+__device__ __forceinline__ void group_norm_row(const float* row, int width, int groups, float eps, const void* weight, int wtype,
+                                               TO* out, float* scratch) {
+  const int gs = width / groups;
+  for (int g = 0; g < groups; ++g) {
+    float sq = 0.f;
+    for (int e = threadIdx.x; e < gs; e += blockDim.x) { const float v = row[g * gs + e]; sq = fmaf(v, v, sq); }
+    const float r = rsqrtf(block_sum(sq, scratch) / (float)gs + eps);
+    for (int e = threadIdx.x; e < gs; e += blockDim.x)
+      out[g * gs + e] = from_f32<TO>(row[g * gs + e] * r * load_as_f32(weight, wtype, g * gs + e));
+  }
+}
+
+// x[r] += mult * delta[r] (written back unless `rows` picks the rows); keep[r] = the updated row (optional, row stride
+// keep_stride); out[b] = the norm in groups of the updated row.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+group_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, float mult, const void* __restrict__ weight, int wtype,
+                     int groups, float eps, TO* __restrict__ out, const int* __restrict__ rows, float* __restrict__ keep,
+                     long long keep_stride, int width) {
+  extern __shared__ float gn_row[];
+  __shared__ float scratch[33];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int b = blockIdx.x;
+  const int r = rows ? rows[b] : b;
+  float* xr = x + (size_t)r * width;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    float v = xr[e];
+    if (delta) v = fmaf(mult, delta[(size_t)r * width + e], v);
+    gn_row[e] = v;
+    if (delta && !rows) xr[e] = v;
+    if (keep) keep[(size_t)r * keep_stride + e] = v;
+  }
+  __syncthreads();
+  group_norm_row<TO>(gn_row, width, groups, eps, weight, wtype, out + (size_t)b * width, scratch);
+}
+
+IFB_EXPORT int ifb_group_rmsnorm(float* x, const float* delta, float mult, const void* weight, int wtype, int groups, float eps,
+                                 void* out, int otype, const int* rows, float* keep, long long keep_stride, int n, int width,
+                                 cudaStream_t stream) {
+  if (n <= 0) return IFB_OK;
+  if (width < 1 || groups < 1 || width % groups) return IFB_ERR_SIZE;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return IFB_ERR_SIZE;
+  if (otype == IFB_BF16) {
+    IFB_ALLOW_SMEM(group_rmsnorm_kernel<__nv_bfloat16>, smem);
+    return ifb_launch(group_rmsnorm_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, x, delta, mult, weight, wtype, groups,
+                      eps, (__nv_bfloat16*)out, rows, keep, keep_stride, width);
+  }
+  if (otype != IFB_F32) return IFB_ERR_DTYPE;
+  IFB_ALLOW_SMEM(group_rmsnorm_kernel<float>, smem);
+  return ifb_launch(group_rmsnorm_kernel<float>, dim3(n), dim3(256), smem, stream, x, delta, mult, weight, wtype, groups, eps,
+                    (float*)out, rows, keep, keep_stride, width);
+}
+
+// ------------------------------------------------------------------------------------------
+// The weighted average over depth.  hist [n, slots, width] holds X_0 .. X_(depth-1) of every token.  The block's result
+// X_depth = x + mult * delta is stored there, x becomes sum_j coeff[j] * X_j (j ascending, j <= depth), and `out` (optional)
+// gets the norm in groups of the new x with the next norm's weight.
+// ------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+depth_average_kernel(float* __restrict__ x, const float* __restrict__ delta, float mult, float* __restrict__ hist, int slots,
+                     int depth, const void* __restrict__ coeff, int ctype, const void* __restrict__ weight, int wtype, int groups,
+                     float eps, TO* __restrict__ out, int width) {
+  extern __shared__ float gn_row[];
+  __shared__ float scratch[33];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int t = blockIdx.x;
+  float* xr = x + (size_t)t * width;
+  float* hr = hist + (size_t)t * slots * width;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    float v = xr[e];
+    if (delta) v = fmaf(mult, delta[(size_t)t * width + e], v);
+    hr[(size_t)depth * width + e] = v;
+    float acc = 0.f;
+    for (int j = 0; j < depth; ++j) acc = fmaf(load_as_f32(coeff, ctype, j), hr[(size_t)j * width + e], acc);
+    acc = fmaf(load_as_f32(coeff, ctype, depth), v, acc);
+    xr[e] = acc;
+    gn_row[e] = acc;
+  }
+  if (out == nullptr) return;
+  __syncthreads();
+  group_norm_row<TO>(gn_row, width, groups, eps, weight, wtype, out + (size_t)t * width, scratch);
+}
+
+IFB_EXPORT int ifb_depth_average(float* x, const float* delta, float mult, float* hist, int slots, int depth, const void* coeff,
+                                 int ctype, const void* weight, int wtype, int groups, float eps, void* out, int otype, int n,
+                                 int width, cudaStream_t stream) {
+  if (n <= 0) return IFB_OK;
+  if (width < 1 || depth < 0 || depth >= slots) return IFB_ERR_SIZE;
+  if (out != nullptr && (groups < 1 || width % groups)) return IFB_ERR_SIZE;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return IFB_ERR_SIZE;
+  if (out == nullptr || otype == IFB_F32) {
+    IFB_ALLOW_SMEM(depth_average_kernel<float>, smem);
+    return ifb_launch(depth_average_kernel<float>, dim3(n), dim3(256), smem, stream, x, delta, mult, hist, slots, depth, coeff,
+                      ctype, weight, wtype, groups, eps, (float*)out, width);
+  }
+  if (otype != IFB_BF16) return IFB_ERR_DTYPE;
+  IFB_ALLOW_SMEM(depth_average_kernel<__nv_bfloat16>, smem);
+  return ifb_launch(depth_average_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, x, delta, mult, hist, slots, depth,
+                    coeff, ctype, weight, wtype, groups, eps, (__nv_bfloat16*)out, width);
+}
+
+// ------------------------------------------------------------------------------------------
+// out_t = h_t + sum_(j <= K) w[:, j] * h_(t - K + j), K = taps - 1, zeros before a sequence's start.  The K inputs before a
+// portion come from the request's state [slots, K, width] (float32, oldest first).  A block per token.  The block of a
+// portion's first token computes every token of the portion that reads the state (its first K) and then replaces the
+// state by the portion's last K inputs (older ones shifted down where the portion is shorter), so that each element of the
+// state is read and written by one thread only; the blocks of those other tokens do nothing.
+// ------------------------------------------------------------------------------------------
+constexpr int CC_MAX_TAPS = 16;
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int wtype, float* __restrict__ state,
+                   const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                   const int* __restrict__ req_index, T* __restrict__ out, int width, int taps) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int t = blockIdx.x, K = taps - 1;
+  const int r = req_index[t];
+  const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
+  if (seq_lens[r] <= 0) {                              // a padding row of a recorded step: it stores and sees nothing
+    for (int e = threadIdx.x; e < width; e += blockDim.x) out[(size_t)t * width + e] = h[(size_t)t * width + e];
+    return;
+  }
+  if (i > 0 && i < K) return;                          // the first token's block computes these
+  if (i >= K) {
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+      float acc = to_f32<T>(h[(size_t)t * width + e]);
+      for (int j = 0; j <= K; ++j)
+        acc = fmaf(load_as_f32(weight, wtype, (size_t)e * taps + j), to_f32<T>(h[(size_t)(t - K + j) * width + e]), acc);
+      out[(size_t)t * width + e] = from_f32<T>(acc);
+    }
+    return;
+  }
+  float* st = state + (size_t)state_slots[r] * (K > 0 ? K : 1) * width;
+  const int head = len < K ? len : K;                  // tokens of the portion that read the state
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    float seq[2 * CC_MAX_TAPS];                        // inputs -K .. head - 1 of the portion, at index + K
+    float w[CC_MAX_TAPS];
+    for (int k = 0; k < K; ++k) seq[k] = st[(size_t)k * width + e];
+    for (int k = 0; k < head; ++k) seq[K + k] = to_f32<T>(h[(size_t)(q0 + k) * width + e]);
+    for (int j = 0; j <= K; ++j) w[j] = load_as_f32(weight, wtype, (size_t)e * taps + j);
+    for (int k = 0; k < head; ++k) {
+      float acc = seq[K + k];
+      for (int j = 0; j <= K; ++j) acc = fmaf(w[j], seq[k + j], acc);
+      out[(size_t)(q0 + k) * width + e] = from_f32<T>(acc);
+    }
+    for (int k = 0; k < K; ++k) {                      // the new state: inputs len - K + k
+      const int idx = len - K + k;
+      st[(size_t)k * width + e] = idx < head ? seq[K + idx] : to_f32<T>(h[(size_t)(q0 + idx) * width + e]);
+    }
+  }
+}
+
+IFB_EXPORT int ifb_causal_conv(const void* h, int dtype, const void* weight, int wtype, float* state, const int* state_slots,
+                               const int* cu_q, const int* seq_lens, const int* req_index, void* out, int tokens, int width,
+                               int taps, cudaStream_t stream) {
+  if (tokens <= 0) return IFB_OK;
+  if (width < 1 || taps < 1 || taps > CC_MAX_TAPS) return IFB_ERR_SIZE;
+  const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+  if (dtype == IFB_BF16)
+    return ifb_launch(causal_conv_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)h, weight,
+                      wtype, state, state_slots, cu_q, seq_lens, req_index, (__nv_bfloat16*)out, width, taps);
+  if (dtype != IFB_F32) return IFB_ERR_DTYPE;
+  return ifb_launch(causal_conv_kernel<float>, dim3(tokens), dim3(threads), 0, stream, (const float*)h, weight, wtype, state,
+                    state_slots, cu_q, seq_lens, req_index, (float*)out, width, taps);
+}
+
+// ------------------------------------------------------------------------------------------
+// After the product q | down(latent, rotated key) | ... of a step (proj, float32, row stride `stride`): per token
+//  * the latent: columns down_col .. + rank, divided by their root mean square, times the norm's weight, stored to its page
+//    stream at slot_mapping (pages [pages, 1, page_size, rank], stored as one row per slot);
+//  * the rotated key part: the next rot columns, their first `dims` entries turned by the token's angles (pair i, i + dims/2;
+//    table [n, dims] holds (cos, sin) pairs), stored to its page stream;
+//  * every head's unrotated query part to q_plain [heads, seg, dim] (head-major: the rows of a head are one segment of the
+//    grouped product that follows) and its rotated part, turned, to q_rot [n, heads, rot] (float32).
+// Block 0 also writes the segments of the grouped products: offsets[h] = h * seg and, for tiles of `tile` rows,
+// tile_head[j] = j / (seg / tile).
+// ------------------------------------------------------------------------------------------
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(256)
+latent_prepare_kernel(const float* __restrict__ proj, long long stride, int heads, int dim, int rot, int rank, int down_col,
+                      const void* __restrict__ norm_w, int wtype, float eps, const float* __restrict__ table, int dims,
+                      TA* __restrict__ q_plain, int seg, float* __restrict__ q_rot, TC* __restrict__ latent_pages,
+                      TC* __restrict__ rot_pages, const int* __restrict__ slot_mapping, int* __restrict__ offsets,
+                      int* __restrict__ tile_head, int tile, int tokens) {
+  __shared__ float scratch[33];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int t = blockIdx.x;
+  if (t == 0) {
+    for (int h = threadIdx.x; h <= heads; h += blockDim.x) offsets[h] = h * seg;
+    if (tile_head != nullptr) {
+      const int per = seg / tile;
+      for (int j = threadIdx.x; j < heads * per; j += blockDim.x) tile_head[j] = j / per;
+    }
+  }
+  const float* row = proj + (size_t)t * stride;
+  const float* tab = table ? table + (size_t)t * dims : nullptr;
+  const int half = dims / 2;
+  // queries
+  const int qw = dim + rot;
+  for (int i = threadIdx.x; i < heads * qw; i += blockDim.x) {
+    const int h = i / qw, c = i - h * qw;
+    if (c < dim) {
+      q_plain[((size_t)h * seg + t) * dim + c] = from_f32<TA>(row[i]);
+    } else {
+      const int d = c - dim;
+      float v = row[i];
+      if (tab != nullptr && d < dims) {
+        const int p = d < half ? d : d - half;
+        const float cs = tab[2 * p], sn = tab[2 * p + 1];
+        v = d < half ? v * cs - row[i + half] * sn : v * cs + row[i - half] * sn;
+      }
+      q_rot[((size_t)t * heads + h) * rot + d] = v;
+    }
+  }
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  // the latent
+  const float* lat = row + down_col;
+  float sq = 0.f;
+  for (int e = threadIdx.x; e < rank; e += blockDim.x) sq = fmaf(lat[e], lat[e], sq);
+  const float r = rsqrtf(block_sum(sq, scratch) / (float)rank + eps);
+  if (slot < 0) return;
+  for (int e = threadIdx.x; e < rank; e += blockDim.x)
+    latent_pages[(size_t)slot * rank + e] = from_f32<TC>(lat[e] * r * load_as_f32(norm_w, wtype, e));
+  // the rotated key part
+  const float* kr = lat + rank;
+  for (int d = threadIdx.x; d < rot; d += blockDim.x) {
+    float v = kr[d];
+    if (tab != nullptr && d < dims) {
+      const int p = d < half ? d : d - half;
+      const float cs = tab[2 * p], sn = tab[2 * p + 1];
+      v = d < half ? v * cs - kr[d + half] * sn : v * cs + kr[d - half] * sn;
+    }
+    rot_pages[(size_t)slot * rot + d] = from_f32<TC>(v);
+  }
+}
+
+IFB_EXPORT int ifb_latent_prepare(const float* proj, long long stride, int heads, int dim, int rot, int rank, int down_col,
+                                  const void* norm_w, int wtype, float eps, const float* table, int dims, void* q_plain, int atype,
+                                  int seg, float* q_rot, void* latent_pages, void* rot_pages, int ctype, const int* slot_mapping,
+                                  int* offsets, int* tile_head, int tile, int tokens, cudaStream_t stream) {
+  if (tokens <= 0) return IFB_OK;
+  if (heads < 1 || dim < 1 || rot < 0 || rank < 1 || seg < tokens || dims < 0 || dims > rot || (dims & 1)) return IFB_ERR_SIZE;
+  if (tile_head != nullptr && (tile < 1 || seg % tile)) return IFB_ERR_SIZE;
+  if (atype != ctype) return IFB_ERR_DTYPE;           // queries and cache share the engine's activation dtype
+#define LP_LAUNCH(TA, TC)                                                                                                        \
+  return ifb_launch(latent_prepare_kernel<TA, TC>, dim3(tokens), dim3(256), 0, stream, proj, stride, heads, dim, rot, rank,      \
+                    down_col, norm_w, wtype, eps, table, dims, (TA*)q_plain, seg, q_rot, (TC*)latent_pages, (TC*)rot_pages,      \
+                    slot_mapping, offsets, tile_head, tile, tokens)
+  if (atype == IFB_BF16) LP_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (atype == IFB_F32) LP_LAUNCH(float, float);
+#undef LP_LAUNCH
+  return IFB_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (gate null: no gate): from the head-major result of a
+// grouped product (float32, `seg` rows per head) to the rows the output product reads.
+// ------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gate_heads_kernel(const float* __restrict__ y, int seg, const float* __restrict__ gate, long long gate_stride,
+                  TO* __restrict__ out, int heads, int vdim) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int t = blockIdx.x, width = heads * vdim;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const int h = i / vdim, v = i - h * vdim;
+    float val = y[((size_t)h * seg + t) * vdim + v];
+    if (gate != nullptr) val *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + i]));
+    out[(size_t)t * width + i] = from_f32<TO>(val);
+  }
+}
+
+IFB_EXPORT int ifb_gate_heads(const float* y, int seg, const float* gate, long long gate_stride, void* out, int otype, int tokens,
+                              int heads, int vdim, cudaStream_t stream) {
+  if (tokens <= 0) return IFB_OK;
+  if (heads < 1 || vdim < 1 || seg < tokens) return IFB_ERR_SIZE;
+  if (otype == IFB_BF16)
+    return ifb_launch(gate_heads_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, y, seg, gate, gate_stride,
+                      (__nv_bfloat16*)out, heads, vdim);
+  if (otype != IFB_F32) return IFB_ERR_DTYPE;
+  return ifb_launch(gate_heads_kernel<float>, dim3(tokens), dim3(256), 0, stream, y, seg, gate, gate_stride, (float*)out, heads,
+                    vdim);
+}

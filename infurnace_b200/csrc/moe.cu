@@ -7,19 +7,71 @@
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------
-// ids[n][j], j < top: the indices of row n's `top` largest logits, largest first, the lower index among equals;
-// gates[n][j]: the softmax over those logits only.  A warp per row; a lane holds the logits e = lane, lane + 32, ...
-// (up to MR_PER_LANE * 32 experts); lane j keeps the j-th chosen logit (up to 32 choices).
+// ids[n][j], j < top: the indices of row n's `top` largest scores, largest first, the lower index among equals.
+// mode 0: the scores are the logits, and gates[n][j] is the softmax over the chosen logits only.  mode 1: the scores are
+// the softmax over all experts, only experts of the `keep` groups (of `groups` equal groups of neighbours) whose best score
+// is largest can be chosen, and gates[n][j] = score * wscale, not renormalised.  A row of logits has `stride` entries, of
+// which the first `experts` are the router's.  A warp per row; a lane holds the logits e = lane, lane + 32, ... (up to
+// MR_PER_LANE * 32 experts); lane j keeps the j-th chosen score (up to 32 choices).
 // ------------------------------------------------------------------------------------------
 constexpr int MR_PER_LANE = 8;
+struct MrMode { int stride, mode, groups, keep; float wscale; };
 __device__ __forceinline__ void mr_route_row(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates,
-                                             int row, int experts, int top, int lane) {
+                                             int row, int experts, int top, int lane, MrMode md) {
   float val[MR_PER_LANE];
 #pragma unroll
   for (int j = 0; j < MR_PER_LANE; ++j) {
     const int e = lane + 32 * j;
-    val[j] = e < experts ? logits[(size_t)row * experts + e] : -INFINITY;
+    val[j] = e < experts ? logits[(size_t)row * md.stride + e] : -INFINITY;
     if (val[j] != val[j]) val[j] = -INFINITY;          // a NaN is never chosen before a number
+  }
+  if (md.mode == 1) {
+    float mx = -INFINITY, tot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MR_PER_LANE; ++j) mx = fmaxf(mx, val[j]);
+    mx = warp_max(mx);
+#pragma unroll
+    for (int j = 0; j < MR_PER_LANE; ++j) { val[j] = lane + 32 * j < experts ? expf(val[j] - mx) : 0.f; tot += val[j]; }
+    tot = warp_sum(tot);
+#pragma unroll
+    for (int j = 0; j < MR_PER_LANE; ++j) val[j] = lane + 32 * j < experts ? val[j] / tot : -INFINITY;
+    if (md.groups > 1 && md.keep < md.groups) {
+      const int gsz = experts / md.groups;
+      float gbest[MR_PER_LANE];                         // lane holds the best score of groups lane, lane + 32, ...
+#pragma unroll
+      for (int j = 0; j < MR_PER_LANE; ++j) gbest[j] = -INFINITY;
+      for (int g = 0; g < md.groups; ++g) {
+        float b = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < MR_PER_LANE; ++j) { const int e = lane + 32 * j; if (e < experts && e / gsz == g) b = fmaxf(b, val[j]); }
+        b = warp_max(b);
+#pragma unroll
+        for (int j = 0; j < MR_PER_LANE; ++j) if ((g & 31) == lane && (g >> 5) == j) gbest[j] = b;
+      }
+      unsigned kept = 0;                                // bit j: this lane's j-th group is kept
+      for (int t = 0; t < md.keep; ++t) {
+        float best = -INFINITY;
+        int best_g = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < MR_PER_LANE; ++j) {
+          const int g = lane + 32 * j;
+          if (g < md.groups && !((kept >> j) & 1u) && (gbest[j] > best || (gbest[j] == best && g < best_g))) { best = gbest[j]; best_g = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+          if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+        }
+        if ((best_g & 31) == lane && best_g < md.groups) kept |= 1u << (best_g >> 5);
+      }
+#pragma unroll
+      for (int j = 0; j < MR_PER_LANE; ++j) {
+        const int e = lane + 32 * j, g = e < experts ? e / gsz : 0;
+        const unsigned bits = __shfl_sync(0xffffffffu, kept, g & 31);
+        if (e < experts && !((bits >> (g >> 5)) & 1u)) val[j] = -INFINITY;
+      }
+    }
   }
   unsigned taken = 0;                                   // bit j: this lane's j-th logit is chosen already
   float first = 0.f, mine = -INFINITY, sum = 0.f;       // lane j < top keeps the j-th chosen logit
@@ -42,6 +94,10 @@ __device__ __forceinline__ void mr_route_row(const float* __restrict__ logits, i
     if (lane == t) mine = best;
     if (lane == 0) ids[(size_t)row * top + t] = best_e < experts ? best_e : 0;
   }
+  if (md.mode == 1) {
+    if (lane < top) gates[(size_t)row * top + lane] = mine * md.wscale;
+    return;
+  }
   const float p = lane < top ? expf(mine - first) : 0.f;
   sum = warp_sum(p);
   if (lane < top) gates[(size_t)row * top + lane] = p / sum;
@@ -49,12 +105,12 @@ __device__ __forceinline__ void mr_route_row(const float* __restrict__ logits, i
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
-                 int top) {
+                 int top, MrMode md) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= rows) return;
-  mr_route_row(logits, ids, gates, row, experts, top, lane);
+  mr_route_row(logits, ids, gates, row, experts, top, lane, md);
 }
 
 // The router and the pair list of a step of few rows (decode) in one launch: one block routes the rows, a warp each in
@@ -62,12 +118,12 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float*
 constexpr int MS_THREADS = 256;
 __global__ void __launch_bounds__(MS_THREADS)
 moe_route_plan_small_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
-                            int top, int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos) {
+                            int top, int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos, MrMode md) {
   __shared__ int cnt[MS_THREADS];
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int row = warp; row < rows; row += MS_THREADS / 32) mr_route_row(logits, ids, gates, row, experts, top, lane);
+  for (int row = warp; row < rows; row += MS_THREADS / 32) mr_route_row(logits, ids, gates, row, experts, top, lane, md);
   __syncthreads();                                 // the block's own writes of ids are visible to it
   const int e = threadIdx.x, pairs = rows * top;
   int mine = 0;
@@ -84,18 +140,29 @@ moe_route_plan_small_kernel(const float* __restrict__ logits, int* __restrict__ 
     if (ids[i] == e) { perm[place] = i; pos[i] = place; ++place; }
 }
 
-IFB_EXPORT int ifb_moe_route_plan_small(const float* logits, int* ids, float* gates, int rows, int experts, int top, int* offsets,
-                                        int* perm, int* pos, cudaStream_t stream) {
-  if (rows <= 0) return IFB_OK;
-  if (experts < 1 || experts > MS_THREADS || top < 1 || top > experts || top > 32 || (long long)rows * top > 4096) return IFB_ERR_SIZE;
-  return ifb_launch(moe_route_plan_small_kernel, dim3(1), dim3(MS_THREADS), 0, stream, logits, ids, gates, rows, experts, top,
-                    offsets, perm, pos);
+static bool mr_mode_ok(const MrMode& md, int experts) {
+  return md.stride >= experts && (md.mode == 0 || md.mode == 1) && md.groups >= 1 && md.keep >= 1 && md.keep <= md.groups &&
+         experts % md.groups == 0;
 }
 
-IFB_EXPORT int ifb_moe_route(const float* logits, int* ids, float* gates, int rows, int experts, int top, cudaStream_t stream) {
+IFB_EXPORT int ifb_moe_route_plan_small(const float* logits, int* ids, float* gates, int rows, int experts, int top, int* offsets,
+                                        int* perm, int* pos, int stride, int mode, int groups, int keep, float wscale,
+                                        cudaStream_t stream) {
+  if (rows <= 0) return IFB_OK;
+  if (experts < 1 || experts > MS_THREADS || top < 1 || top > experts || top > 32 || (long long)rows * top > 4096) return IFB_ERR_SIZE;
+  const MrMode md{stride, mode, groups, keep, wscale};
+  if (!mr_mode_ok(md, experts)) return IFB_ERR_ARG;
+  return ifb_launch(moe_route_plan_small_kernel, dim3(1), dim3(MS_THREADS), 0, stream, logits, ids, gates, rows, experts, top,
+                    offsets, perm, pos, md);
+}
+
+IFB_EXPORT int ifb_moe_route(const float* logits, int* ids, float* gates, int rows, int experts, int top, int stride, int mode,
+                             int groups, int keep, float wscale, cudaStream_t stream) {
   if (rows <= 0) return IFB_OK;
   if (experts < 1 || experts > 32 * MR_PER_LANE || top < 1 || top > experts || top > 32) return IFB_ERR_SIZE;
-  return ifb_launch(moe_route_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, logits, ids, gates, rows, experts, top);
+  const MrMode md{stride, mode, groups, keep, wscale};
+  if (!mr_mode_ok(md, experts)) return IFB_ERR_ARG;
+  return ifb_launch(moe_route_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, logits, ids, gates, rows, experts, top, md);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -626,25 +693,31 @@ IFB_EXPORT int ifb_moe_linear(const void* x, int x_dtype, const void* w, int w_d
 }
 
 // ------------------------------------------------------------------------------------------
-// out[n][f] = sum_j gates[n][j] * y[pos[n * top + j]][f], j ascending, float32.
+// out[n][f] = sum_j gates[n][j] * y[pos[n * top + j]][f], j ascending, float32; then, with `shared` (the result of an
+// expert that every row runs), + g * shared[n][f], g = sigmoid(shared_logit[n * logit_stride]) or 1 without a logit.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ gates,
-                   float* __restrict__ out, int top, int width) {
+                   float* __restrict__ out, int top, int width, const float* __restrict__ shared,
+                   const float* __restrict__ shared_logit, int logit_stride) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int n = blockIdx.x;
+  float g = 1.f;
+  if (shared != nullptr && shared_logit != nullptr) g = 1.f / (1.f + expf(-shared_logit[(size_t)n * logit_stride]));
   for (int f = threadIdx.x; f < width; f += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
       acc = fmaf(gates[(size_t)n * top + j], y[(size_t)pos[(size_t)n * top + j] * width + f], acc);
+    if (shared != nullptr) acc = fmaf(g, shared[(size_t)n * width + f], acc);
     out[(size_t)n * width + f] = acc;
   }
 }
 
 IFB_EXPORT int ifb_moe_combine(const float* y, const int* pos, const float* gates, float* out, int rows, int top, int width,
-                               cudaStream_t stream) {
+                               const float* shared, const float* shared_logit, int logit_stride, cudaStream_t stream) {
   if (rows <= 0 || width <= 0) return IFB_OK;
   if (top < 1) return IFB_ERR_SIZE;
-  return ifb_launch(moe_combine_kernel, dim3(rows), dim3(256), 0, stream, y, pos, gates, out, top, width);
+  return ifb_launch(moe_combine_kernel, dim3(rows), dim3(256), 0, stream, y, pos, gates, out, top, width, shared, shared_logit,
+                    logit_stride);
 }

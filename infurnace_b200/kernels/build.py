@@ -40,6 +40,9 @@ LIBRARIES: Dict[str, tuple] = {
     # sandwich-norm blocks, recurrences over a matrix state or an element-wise one, attention with rotated values over
     # page streams, routed experts
     "hybrid": (["sandwich.cu", "linear_scan.cu", "attention_streams.cu", "moe.cu"], []),
+    # decoders with latent attention: norms in groups, the short causal convolution, the average over depth, the
+    # preparation of queries and latents, attention over cached latents, the output gate
+    "latent": (["latent.cu", "attention_latent.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }
@@ -198,7 +201,7 @@ def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
     from concurrent.futures import ThreadPoolExecutor
     jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None), ("attention_tc", None),
-            ("mixers", None), ("hybrid", None)] + DEFAULT_VARIANTS
+            ("mixers", None), ("hybrid", None), ("latent", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
         built = list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))
     # objects of older sources are never loaded (their names carry another hash); take them out of the folder

@@ -112,6 +112,7 @@ class CudaKernels:
         self.scan_blocked_calls = 0                                                    # which the recurrence runs in blocks
         self._scan_scratch = None
         self._hyb = None               # the library of sandwich-norm blocks, state recurrences, stream attention, routed experts
+        self._lat = None               # the library of decoders with latent attention
         self._ls_scratch = None
         self._gu_scratch = None
         self.gated_unit_chunked_calls = 0
@@ -880,13 +881,13 @@ class CudaKernels:
             m.ifb_paged_attention_streams.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
                                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                       c_int, c_float, c_int, c_void_p, c_int, c_void_p]
-            m.ifb_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
             m.ifb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
             m.ifb_moe_linear.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_void_p]
-            m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
             m.ifb_moe_route_plan_small.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                                   c_void_p]
+                                                   c_int, c_int, c_int, c_int, c_float, c_void_p]
             m.ifb_moe_plan_padded.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
             m.ifb_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         return self._hyb
@@ -1120,24 +1121,42 @@ class CudaKernels:
             seq_lens.data_ptr(), out.data_ptr(), n, r, H, G, d, dv, pk[2], float(scale), int(window), _ptr(out_table),
             int(bool(out_interleaved)), self._stream()), "paged_attention_streams")
 
-    def moe_route(self, logits, top, ids, gates):
-        """ids[n] = the indices of row n's ``top`` largest logits, largest first (the lower index among equals);
-        gates[n] = the softmax over those logits (csrc/moe.cu)."""
+    @staticmethod
+    def _route_mode(logits, experts, scoring, groups, weight_scale):
+        """(experts, stride, mode, group count, groups kept, weight scale) of a router call: ``experts`` None means every
+        column of ``logits`` is an expert's."""
+        if scoring not in ("chosen", "all"):
+            raise KernelError(f"moe_route: scoring {scoring!r}; known: chosen, all")
+        count, keep = groups if groups else (1, 1)
+        if groups and scoring != "all":
+            raise KernelError("moe_route: groups of experts limit the choice only with scoring 'all'")
+        return (int(experts) if experts is not None else logits.shape[1], logits.shape[1], 1 if scoring == "all" else 0,
+                int(count), int(keep), float(weight_scale))
+
+    def moe_route(self, logits, top, ids, gates, experts=None, scoring="chosen", groups=None, weight_scale=1.0):
+        """ids[n] = the indices of row n's ``top`` largest scores, largest first (the lower index among equals).  scoring
+        "chosen": the scores are the logits and gates[n] = the softmax over the chosen logits.  scoring "all": the scores are
+        the softmax over all experts, gates[n] = score * weight_scale, and with ``groups`` = (count, keep) only experts of the
+        ``keep`` groups of neighbours with the largest best score can be chosen.  ``experts``: the first that many columns of
+        ``logits`` are the router's (the rest belong to someone else).  (csrc/moe.cu)"""
         _dense(logits, "logits", torch.float32), _dense(ids, "ids", torch.int32), _dense(gates, "gates", torch.float32)
-        n, experts = logits.shape
+        n = logits.shape[0]
+        experts, stride, mode, count, keep, ws = self._route_mode(logits, experts, scoring, groups, weight_scale)
         if ids.shape != (n, top) or gates.shape != (n, top):
             raise KernelError("moe_route: ids and gates are [rows, top]")
         self.launches += 1
-        _check(self._hyb_lib().ifb_moe_route(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top),
-                                             self._stream()), "moe_route")
+        _check(self._hyb_lib().ifb_moe_route(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top), stride, mode,
+                                             count, keep, ws, self._stream()), "moe_route")
 
     MOE_SMALL_PAIRS = 512      # up to here the router and the pair list are one launch of one block
 
-    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos):
+    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos, experts=None, scoring="chosen", groups=None,
+                       weight_scale=1.0):
         """:meth:`moe_route` and :meth:`moe_plan` of a step; one launch where the step has few pairs (decode)."""
-        n, experts = logits.shape
+        n = logits.shape[0]
+        experts, stride, mode, count, keep, ws = self._route_mode(logits, experts, scoring, groups, weight_scale)
         if n * top > self.MOE_SMALL_PAIRS or experts > 256:
-            self.moe_route(logits, top, ids, gates)
+            self.moe_route(logits, top, ids, gates, experts=experts, scoring=scoring, groups=groups, weight_scale=weight_scale)
             return self.moe_plan(ids, experts, offsets, perm, pos)
         _dense(logits, "logits", torch.float32), _dense(ids, "ids", torch.int32), _dense(gates, "gates", torch.float32)
         _dense(offsets, "offsets", torch.int32), _dense(perm, "perm", torch.int32), _dense(pos, "pos", torch.int32)
@@ -1146,7 +1165,8 @@ class CudaKernels:
             raise KernelError("moe_route_plan: sizes of ids, gates, offsets, perm and pos do not match")
         self.launches += 1
         _check(self._hyb_lib().ifb_moe_route_plan_small(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top),
-                                                        offsets.data_ptr(), perm.data_ptr(), pos.data_ptr(), self._stream()),
+                                                        offsets.data_ptr(), perm.data_ptr(), pos.data_ptr(), stride, mode, count,
+                                                        keep, ws, self._stream()),
                "moe_route_plan")
 
     def moe_plan(self, ids, num_experts, offsets, perm, pos):
@@ -1245,17 +1265,169 @@ class CudaKernels:
                                               1 if gated else 0, tile_expert.data_ptr(), self._dev_err.data_ptr(), self._stream()),
                "moe_linear_grouped")
 
-    def moe_combine(self, y, pos, gates, out):
+    def moe_combine(self, y, pos, gates, out, shared=None, shared_logit=None):
         """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32 (y may hold more rows than pairs: a
-        padded list)."""
+        padded list).  ``shared`` [n, width] float32: + shared[n], times sigmoid(shared_logit[n]) when ``shared_logit`` (a
+        column of a float32 matrix) is given."""
         _dense(y, "y", torch.float32), _dense(pos, "pos", torch.int32), _dense(gates, "gates", torch.float32)
         _dense(out, "out", torch.float32)
         n, top = gates.shape
         if pos.numel() != n * top or y.shape[0] < n * top or y.shape[1] != out.shape[1] or out.shape[0] != n:
             raise KernelError("moe_combine: sizes of y, pos, gates and out do not match")
+        stride = 0
+        if shared is not None:
+            if _dense(shared, "shared", torch.float32).shape != out.shape:
+                raise KernelError("moe_combine: shared has the shape of out")
+            if shared_logit is not None:
+                if shared_logit.dtype != torch.float32 or shared_logit.dim() != 1 or shared_logit.shape[0] != n:
+                    raise KernelError("moe_combine: shared_logit is one float32 number per row")
+                stride = shared_logit.stride(0)
         self.launches += 1
         _check(self._hyb_lib().ifb_moe_combine(y.data_ptr(), pos.data_ptr(), gates.data_ptr(), out.data_ptr(), n, top,
-                                               out.shape[1], self._stream()), "moe_combine")
+                                               out.shape[1], _ptr(shared), _ptr(shared_logit) if shared is not None else None,
+                                               stride, self._stream()), "moe_combine")
+
+    # ------------------------------------------------------------------ decoders with latent attention (csrc/latent.cu)
+    def _lat_lib(self):
+        if self._lat is None:
+            m = self._lat = load_library("latent", progress=self._progress)
+            m.ifb_group_rmsnorm.argtypes = [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
+                                            c_void_p, c_longlong, c_int, c_int, c_void_p]
+            m.ifb_depth_average.argtypes = [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                            c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_causal_conv.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_latent_prepare.argtypes = [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float,
+                                             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_void_p]
+            m.ifb_gate_heads.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_latent_attention.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_float, c_int, c_void_p]
+        return self._lat
+
+    def group_rmsnorm(self, x, weight, groups, eps, out, delta=None, mult=1.0, rows=None, keep=None):
+        """The RMS norm in ``groups`` equal parts of the row, each with its own statistic, times ``weight``.  With ``delta``
+        the rows of x (float32) first become x + mult * delta (written back unless ``rows`` picks the rows that are normed).
+        ``keep`` [n, width] (a float32 view whose rows may be strided) also gets the updated rows."""
+        _dense(x, "x", torch.float32), _dense(weight, "weight"), _dense(out, "out")
+        n, width = x.shape
+        m = n if rows is None else _dense(rows, "rows", torch.int32).numel()
+        if out.shape != (m, width) or weight.numel() != width:
+            raise KernelError("group_rmsnorm: sizes of x, weight and out do not match")
+        if delta is not None and _dense(delta, "delta", torch.float32).shape != x.shape:
+            raise KernelError("group_rmsnorm: delta has the shape of x")
+        stride = 0
+        if keep is not None:
+            if keep.dtype != torch.float32 or keep.shape != x.shape or keep.stride(1) != 1 or rows is not None:
+                raise KernelError("group_rmsnorm: keep is a float32 view of x's shape with unit stride along the row")
+            stride = keep.stride(0)
+        self.launches += 1
+        _check(self._lat_lib().ifb_group_rmsnorm(x.data_ptr(), _ptr(delta), float(mult), weight.data_ptr(), _code(weight), int(groups),
+                                                 float(eps), out.data_ptr(), _code(out), _ptr(rows), _ptr(keep), stride, m, width,
+                                                 self._stream()), "group_rmsnorm")
+
+    def depth_average(self, x, delta, mult, hist, depth, coeff, out=None, next_weight=None, groups=1, eps=0.0):
+        """hist [n, slots, width] float32 holds X_0 .. X_(depth-1) of every token.  X_depth = x + mult * delta is stored
+        there and x becomes sum_j coeff[j] * X_j, j = 0 .. depth; ``out`` gets the norm in groups of the new x with
+        ``next_weight``."""
+        _dense(x, "x", torch.float32), _dense(hist, "hist", torch.float32), _dense(coeff, "coeff")
+        n, width = x.shape
+        if hist.dim() != 3 or hist.shape[0] != n or hist.shape[2] != width or not 0 <= depth < hist.shape[1] or coeff.numel() != depth + 1:
+            raise KernelError("depth_average: sizes of x, hist and coeff do not match")
+        if delta is not None and _dense(delta, "delta", torch.float32).shape != x.shape:
+            raise KernelError("depth_average: delta has the shape of x")
+        if (out is None) != (next_weight is None) or (out is not None and (_dense(out, "out").shape != x.shape
+                                                                            or _dense(next_weight, "next_weight").numel() != width)):
+            raise KernelError("depth_average: out and next_weight come together and have x's shape and row length")
+        self.launches += 1
+        _check(self._lat_lib().ifb_depth_average(x.data_ptr(), _ptr(delta), float(mult), hist.data_ptr(), hist.shape[1], int(depth),
+                                                 coeff.data_ptr(), _code(coeff), _ptr(next_weight),
+                                                 _code(next_weight) if next_weight is not None else 0, int(groups), float(eps),
+                                                 _ptr(out), _code(out) if out is not None else 0, n, width, self._stream()),
+               "depth_average")
+
+    def causal_conv(self, h, weight, state, state_slots, cu_q, seq_lens, req_index, out):
+        """out_t = h_t + sum_j weight[:, j] * h_(t - taps + 1 + j) over each request's tokens; the taps - 1 inputs before a
+        portion come from state[slot] ([slots, taps - 1, width] float32), which then takes the portion's last inputs."""
+        _dense(h, "h"), _dense(weight, "weight"), _dense(state, "state", torch.float32), _dense(out, "out", h.dtype)
+        n, width = h.shape
+        taps = weight.shape[1]
+        if weight.shape[0] != width or out.shape != h.shape or state.shape[1:] != (max(taps - 1, 1), width):
+            raise KernelError("causal_conv: sizes of h, weight, state and out do not match")
+        self.launches += 1
+        _check(self._lat_lib().ifb_causal_conv(h.data_ptr(), _code(h), weight.data_ptr(), _code(weight), state.data_ptr(),
+                                               state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), req_index.data_ptr(),
+                                               out.data_ptr(), n, width, taps, self._stream()), "causal_conv")
+
+    def latent_prepare(self, proj, heads, dim, rot, rank, down_col, norm_weight, eps, table, dims, q_plain, q_rot, latent_pages,
+                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0):
+        """From a step's product q | latent, rotated key | ... (proj, float32): the normalised latent and the turned rotated
+        key part into their page streams ([pages, 1, page_size, width]) at slot_mapping (None: nothing is stored), the
+        heads' unrotated query parts head-major into q_plain [heads, seg, dim], their turned rotated parts into q_rot
+        [n, heads, rot] (float32).  offsets [heads + 1] gets the segments h * seg of the grouped products that follow,
+        tile_head [heads * seg / tile] the head of every tile of rows.  table [n, dims]: (cos, sin) pairs (None: no turn)."""
+        _dense(proj, "proj", torch.float32), _dense(q_plain, "q_plain"), _dense(latent_pages, "latent_pages", q_plain.dtype)
+        _dense(offsets, "offsets", torch.int32), _dense(norm_weight, "norm_weight")
+        n, stride = proj.shape
+        seg = q_plain.shape[1]
+        if q_plain.shape != (heads, seg, dim) or seg < n or offsets.numel() != heads + 1 or norm_weight.numel() != rank \
+                or latent_pages.shape[1] != 1 or latent_pages.shape[3] != rank or heads * (dim + rot) > down_col \
+                or down_col + rank + rot > stride:
+            raise KernelError("latent_prepare: sizes of proj, q_plain, latent_pages and offsets do not match")
+        if rot:
+            if _dense(q_rot, "q_rot", torch.float32).shape != (n, heads, rot) or _dense(rot_pages, "rot_pages", q_plain.dtype).shape[3] != rot \
+                    or rot_pages.shape[:3] != latent_pages.shape[:3]:
+                raise KernelError("latent_prepare: q_rot is [n, heads, rot] and rot_pages has rot entries per slot")
+        if table is not None and (_dense(table, "table", torch.float32).shape != (n, dims) or dims > rot or dims % 2):
+            raise KernelError("latent_prepare: table is [n, dims] with dims even and at most rot")
+        if tile_head is not None and (_dense(tile_head, "tile_head", torch.int32).numel() * tile != heads * seg):
+            raise KernelError("latent_prepare: tile_head has an entry for every tile of rows")
+        self.launches += 1
+        _check(self._lat_lib().ifb_latent_prepare(proj.data_ptr(), stride, heads, dim, rot, rank, down_col, norm_weight.data_ptr(),
+                                                  _code(norm_weight), float(eps), _ptr(table), int(dims) if table is not None else 0,
+                                                  q_plain.data_ptr(), _code(q_plain), seg, _ptr(q_rot) if rot else None,
+                                                  latent_pages.data_ptr(), _ptr(rot_pages) if rot else None, _code(latent_pages),
+                                                  _ptr(slot_mapping), offsets.data_ptr(), _ptr(tile_head), int(tile), n,
+                                                  self._stream()), "latent_prepare")
+
+    def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
+                         window, tokens):
+        """Attention of every head over the request's cached latents (the absorbed form): q_lat [heads, seg, rank] float32,
+        q_rot [n, heads, rot] float32 (None without a rotated part), out [heads, seg, rank] = the softmax-weighted sum of
+        latents per head.  ``sink`` [heads]: exp of it joins the denominator.  ``window`` 0: every earlier position."""
+        _dense(q_lat, "q_lat", torch.float32), _dense(latent_pages, "latent_pages"), _dense(out, "out", latent_pages.dtype)
+        heads, seg, rank = q_lat.shape
+        rot = rot_pages.shape[3] if rot_pages is not None else 0
+        if out.shape != q_lat.shape or latent_pages.shape[1] != 1 or latent_pages.shape[3] != rank or seg < tokens:
+            raise KernelError("latent_attention: sizes of q_lat, latent_pages and out do not match")
+        if rot and (_dense(q_rot, "q_rot", torch.float32).shape != (tokens, heads, rot) or _dense(rot_pages, "rot_pages", latent_pages.dtype).shape[:3] != latent_pages.shape[:3]):
+            raise KernelError("latent_attention: q_rot is [n, heads, rot] and rot_pages lies beside latent_pages")
+        if sink is not None and _dense(sink, "sink").numel() != heads:
+            raise KernelError("latent_attention: sink has one number per head")
+        self.launches += 1
+        _check(self._lat_lib().ifb_latent_attention(q_lat.data_ptr(), _ptr(q_rot) if rot else None, seg, latent_pages.data_ptr(),
+                                                    _ptr(rot_pages) if rot else None, _code(latent_pages), block_tables.data_ptr(),
+                                                    block_tables.stride(0), latent_pages.shape[2], cu_q.data_ptr(), seq_lens.data_ptr(),
+                                                    req_index.data_ptr(), _ptr(sink), _code(sink) if sink is not None else 0,
+                                                    out.data_ptr(), _code(out), int(tokens), heads, rank, rot, float(scale),
+                                                    int(window or 0), self._stream()), "latent_attention")
+
+    def gate_heads(self, y, gate, out, tokens):
+        """out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (gate None: no gate); y [heads, seg, vdim]
+        float32, gate a float32 view [n, heads * vdim] whose rows may be strided."""
+        _dense(y, "y", torch.float32), _dense(out, "out")
+        heads, seg, vdim = y.shape
+        if out.shape != (tokens, heads * vdim) or seg < tokens:
+            raise KernelError("gate_heads: out is [tokens, heads * vdim]")
+        stride = 0
+        if gate is not None:
+            if gate.dtype != torch.float32 or gate.shape != out.shape or gate.stride(1) != 1:
+                raise KernelError("gate_heads: gate is a float32 view of out's shape with unit stride along the row")
+            stride = gate.stride(0)
+        self.launches += 1
+        _check(self._lat_lib().ifb_gate_heads(y.data_ptr(), seg, _ptr(gate), stride, out.data_ptr(), _code(out), int(tokens), heads,
+                                              vdim, self._stream()), "gate_heads")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

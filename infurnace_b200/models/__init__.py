@@ -7,3 +7,4 @@ from .registry import (  # noqa: F401
 from . import qwen3  # noqa: F401  (registers "Qwen3ForCausalLM")
 from . import kafunex  # noqa: F401  (registers "Kafunex")
 from . import lunelorn  # noqa: F401  (registers "Lunelorn")
+from . import filorax  # noqa: F401  (registers "Filorax")

@@ -2,5 +2,5 @@
 implementations of the descriptions in ``infurnace_b200.config.specs``."""
 from .registry import Runtime, build_part, register_part  # noqa: F401
 from . import norm, rotary, attention, mlp, block, model, recurrence, talking_attention  # noqa: F401
-from . import rotary_value_attention, parallel, experts  # noqa: F401
+from . import rotary_value_attention, parallel, experts, conv, latent_attention  # noqa: F401
 from .model import DecoderModel  # noqa: F401

@@ -3,7 +3,9 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, StreamInjectSpec, TokenSideSpec
+from ..config.specs import (
+    DepthAverageBlockSpec, LayerCall, PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, StreamInjectSpec, TokenSideSpec,
+)
 from .parallel import WeightedSum
 from .registry import Folded, build_part, register_part
 
@@ -224,6 +226,90 @@ class SandwichBlock:
 
 
 register_part(SandwichBlockSpec, SandwichBlock)
+
+
+# key of ``ctx.shared`` under which the blocks that average over depth keep every token's earlier block results of the step
+DEPTH_HISTORY = ("depth_history",)
+
+
+class DepthAverageBlock:
+    """x += m * mixer(conv1(norm1(x))); x += m * ffn(conv2(norm2(x))); then x <- sum_j a[j] * X_j over the embedding's
+    output X_0 and the results X_1 .. of all blocks so far, this one's included.
+
+    The X_j of a step's tokens live in one float32 buffer [tokens, depths, hidden] shared by the blocks of the model
+    (scratch of the step, not state: an average reads the same token's rows only).  The block at depth 0 puts the
+    embedding's output there while it forms its first norm.  The mixer's delta is added in the kernel of the second
+    norm; the last delta is added in the averaging kernel, which stores the block's result, writes the average over x
+    and, when a block of this kind follows, also that block's first norm of the new x (it gets a :class:`ReadyInput`).
+    Each convolution keeps its last inputs in a state entry of its own: entry 0 of the call's cache is the mixer's,
+    entries 1 and 2 the convolutions'.  x is up to date when the block returns."""
+
+    hands_over_input = True
+
+    def __init__(self, spec: DepthAverageBlockSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.mixer_norm = build_part(spec.mixer_norm, weights, runtime)
+        self.mixer = build_part(spec.mixer, weights, runtime)
+        self.mixer_conv = build_part(spec.mixer_conv, weights, runtime) if spec.mixer_conv is not None else None
+        has_ffn = spec.ffn is not None
+        self.ffn = build_part(spec.ffn, weights, runtime) if has_ffn else None
+        self.ffn_norm = build_part(spec.ffn_norm, weights, runtime) if has_ffn else None
+        self.ffn_conv = build_part(spec.ffn_conv, weights, runtime) if has_ffn and spec.ffn_conv is not None else None
+        self.average = weights[spec.average] if spec.average is not None else None
+
+    @property
+    def graph_safe(self):
+        parts = [self.mixer] + [p for p in (self.ffn, self.mixer_conv, self.ffn_conv) if p is not None]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
+    def _history(self, x, ctx):
+        """The step's [tokens, depths, hidden] buffer; every block asks for the same one (``depths`` is the plan's)."""
+        hist = ctx.shared.get(DEPTH_HISTORY)
+        if hist is None:
+            if self.spec.depth != 0:
+                raise RuntimeError("a block that averages over depth found no history: the block at depth 0 has not run in this step")
+            hist = ctx.buffer("depth_history", (x.shape[0], self.spec.depths + 1, x.shape[1]), torch.float32)
+            ctx.shared[DEPTH_HISTORY] = hist
+        return hist
+
+    def forward(self, x, pending, ctx, call, next_layer=None):
+        s, k = self.spec, self.k
+        m = s.residual_mult
+        hist = self._history(x, ctx) if self.average is not None else None
+        if isinstance(pending, ReadyInput):          # the block before this one wrote our first norm already
+            h = pending.values
+        else:
+            if isinstance(pending, Folded):
+                raise TypeError("a block that averages over depth cannot take a folded norm from the block before it")
+            if hist is not None and s.depth != 0:
+                raise RuntimeError("the average over depth needs every earlier block's result: only the block at depth 0 may "
+                                   "start from a plain stream")
+            h = ctx.buffer("h", x.shape, self.rt.act_dtype)
+            self.mixer_norm.forward(x, h, delta=pending, keep=hist[:, 0] if hist is not None else None)
+        if self.mixer_conv is not None:
+            h = self.mixer_conv.forward(h, ctx, (call.cache, 1))
+        d = self.mixer.forward(h, ctx, LayerCall(call.layer, (call.cache, 0), call.store))
+        if self.ffn is not None:
+            h = ctx.buffer("h", x.shape, self.rt.act_dtype)
+            self.ffn_norm.forward(x, h, delta=d, mult=m)
+            if self.ffn_conv is not None:
+                h = self.ffn_conv.forward(h, ctx, (call.cache, 2))
+            d = self.ffn.forward(h, ctx)
+        ahead = next_layer.mixer_norm if isinstance(next_layer, DepthAverageBlock) else None
+        out = ctx.buffer("h", x.shape, self.rt.act_dtype) if ahead is not None else None
+        if hist is not None:
+            k.depth_average(x, d, m, hist, s.depth + 1, self.average, out=out, next_weight=ahead.weight if ahead is not None else None,
+                            groups=ahead.spec.groups if ahead is not None else 1, eps=ahead.spec.eps if ahead is not None else 0.0)
+        elif ahead is not None:
+            ahead.forward(x, out, delta=d, mult=m)
+        else:
+            k.scaled_sum(x, d, m)
+        return ReadyInput(out) if ahead is not None else None
+
+
+register_part(DepthAverageBlockSpec, DepthAverageBlock)
 
 
 class StreamInject:

@@ -18,7 +18,12 @@ class RoutedExperts:
     along a leading axis, and one kernel sums each token's results in the order of its choices, in float32.  bfloat16
     steps of more than 256 pairs (prompts) take the tcgen05 kernel in its grouped mode, over a list whose segments are
     padded to that kernel's tile of 128 rows (``_forward_padded``); fewer pairs, float32 and odd sizes the kernels of
-    csrc/moe.cu."""
+    csrc/moe.cu.
+
+    The description's ``scoring``, ``groups`` and ``weight_scale`` go to the router kernel as they are.  A ``shared``
+    expert is two dense products on every row; its result joins the weighted sum in the combining kernel, times
+    sigmoid of the row's ``shared_gate`` logit when there is one.  That logit is one more row of the router's matrix, so
+    it costs no product of its own."""
 
     graph_safe = True
 
@@ -29,6 +34,17 @@ class RoutedExperts:
         self.rt = runtime
         self.k = runtime.kernels
         self.router = weights[spec.router]
+        self.w_shared_gate_up = self.w_shared_down = None
+        if spec.shared is not None:
+            if spec.shared.activation != "silu":
+                raise ModelConfigError(f"activation {spec.shared.activation!r}: only 'silu' has a kernel")
+            self.w_shared_gate_up = torch.cat((weights[spec.shared.gate_proj], weights[spec.shared.up_proj]), dim=0).contiguous()
+            self.w_shared_down = weights[spec.shared.down_proj]
+            if spec.shared_gate is not None:
+                self.router = torch.cat((self.router, weights[spec.shared_gate].to(self.router.dtype)), dim=0).contiguous()
+        elif spec.shared_gate is not None:
+            raise ModelConfigError("a gate of the shared expert needs a shared expert")
+        self.route_args = dict(scoring=spec.scoring, groups=spec.groups, weight_scale=spec.weight_scale)
         self.w_gate_up = torch.stack([torch.cat((weights[g], weights[u]), dim=0) for g, u, _ in spec.experts], dim=0).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in spec.experts], dim=0).contiguous()
         self.num_experts = len(spec.experts)
@@ -36,28 +52,41 @@ class RoutedExperts:
     def forward(self, h, ctx, fold=None):
         s, k, E = self.spec, self.k, self.num_experts
         n = h.shape[0]
-        logits = ctx.buffer("moe_logits", (n, E), torch.float32)
+        logits = ctx.buffer("moe_logits", (n, self.router.shape[0]), torch.float32)
         k.linear(h, self.router, logits)
+        shared = self._shared(h, ctx, logits)
         ids = ctx.buffer("moe_ids", (n, s.top), torch.int32)
         gates = ctx.buffer("moe_gates", (n, s.top), torch.float32)
         pairs = n * s.top
         ok = getattr(k, "moe_grouped_tc_ok", None)
         if ok is not None and ok(pairs, h.dtype, self.w_gate_up, self.w_down):
-            k.moe_route(logits, s.top, ids, gates)
-            return self._forward_padded(h, ctx, ids, gates)
+            k.moe_route(logits, s.top, ids, gates, experts=E, **self.route_args)
+            return self._forward_padded(h, ctx, ids, gates, shared)
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32, rows=E + 1)
         perm = ctx.buffer("moe_perm", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
         pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
-        k.moe_route_plan(logits, s.top, ids, gates, offsets, perm, pos)        # one launch for a step of few pairs
+        k.moe_route_plan(logits, s.top, ids, gates, offsets, perm, pos, experts=E, **self.route_args)   # one launch for few pairs
         act = ctx.buffer("moe_act", (pairs, s.intermediate_size), self.rt.act_dtype, rows=ctx.max_rows * s.top)
         k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
         y = ctx.buffer("moe_y", (pairs, s.hidden_size), torch.float32, rows=ctx.max_rows * s.top)
         k.moe_linear(act, self.w_down, offsets, None, 1, y)
         delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
-        k.moe_combine(y, pos, gates, delta)
+        k.moe_combine(y, pos, gates, delta, *shared)
         return delta
 
-    def _forward_padded(self, h, ctx, ids, gates):
+    def _shared(self, h, ctx, logits):
+        """(result of the shared expert [n, hidden] float32, its gate's logits [n]) or (None, None)."""
+        s = self.spec
+        if s.shared is None:
+            return None, None
+        n = h.shape[0]
+        act = ctx.buffer("moe_shared_act", (n, s.shared.intermediate_size), self.rt.act_dtype)
+        self.k.linear(h, self.w_shared_gate_up, act, epilogue="silu_gate")
+        out = ctx.buffer("moe_shared", (n, s.hidden_size), torch.float32)
+        self.k.linear(act, self.w_shared_down, out)
+        return out, (logits[:, self.num_experts] if s.shared_gate is not None else None)
+
+    def _forward_padded(self, h, ctx, ids, gates, shared=(None, None)):
         """A prompt's experts on the tcgen05 kernel: the pair list with every expert's segment padded to the kernel's row
         tile, the tokens' rows gathered into that order, the two products as grouped launches whose row tiles each belong to
         one expert, the weighted sum through the padded places."""
@@ -77,7 +106,7 @@ class RoutedExperts:
         y = ctx.buffer("moe_y_padded", (places, s.hidden_size), torch.float32, rows=cap)
         k.moe_linear_grouped(act, self.w_down, tiles, y)
         delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
-        k.moe_combine(y, pos, gates, delta)
+        k.moe_combine(y, pos, gates, delta, *shared)
         return delta
 
 

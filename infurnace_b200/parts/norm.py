@@ -1,7 +1,7 @@
 """RMSNorm with the residual addition folded in."""
 from __future__ import annotations
 
-from ..config.specs import RMSNormSpec, ScalarRMSNormSpec
+from ..config.specs import GroupRMSNormSpec, RMSNormSpec, ScalarRMSNormSpec
 from .registry import register_part
 
 
@@ -49,3 +49,24 @@ class ScalarRMSNorm:
 
 
 register_part(ScalarRMSNormSpec, ScalarRMSNorm)
+
+
+class GroupRMSNorm:
+    """The RMS norm in groups: the row in ``groups`` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), the whole times the weight; statistics in float32.  With ``delta`` the float32 stream first
+    becomes x + mult * delta (in place, unless ``rows`` picks the rows that are normed); ``keep`` also gets the updated
+    rows."""
+
+    graph_safe = True
+
+    def __init__(self, spec: GroupRMSNormSpec, weights, runtime):
+        self.spec = spec
+        self.weight = weights[spec.weight]
+        self.k = runtime.kernels
+
+    def forward(self, x, out, delta=None, rows=None, mult=1.0, keep=None):
+        self.k.group_rmsnorm(x, self.weight, self.spec.groups, self.spec.eps, out, delta=delta, mult=mult, rows=rows, keep=keep)
+        return out
+
+
+register_part(GroupRMSNormSpec, GroupRMSNorm)

@@ -480,17 +480,36 @@ class ReferenceKernels:
                 out[t] = o.reshape(H * dv).to(out.dtype)
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, logits, top, ids, gates):
-        """ids[n] = the ``top`` largest logits' indices, largest first (the lower index among equals);
-        gates[n] = softmax over those logits."""
-        val, idx = torch.sort(logits.to(self.cd), dim=-1, descending=True, stable=True)
-        ids.copy_(idx[:, :top].to(ids.dtype))
-        gates.copy_(torch.softmax(val[:, :top], dim=-1).to(gates.dtype))
+    def moe_route(self, logits, top, ids, gates, experts=None, scoring="chosen", groups=None, weight_scale=1.0):
+        """ids[n] = the ``top`` largest scores' indices, largest first (the lower index among equals).  scoring "chosen":
+        scores are the logits, gates[n] = softmax over the chosen logits.  scoring "all": scores are the softmax over all
+        experts, limited to the ``keep`` groups of neighbours with the largest best score when ``groups`` = (count, keep);
+        gates[n] = score * weight_scale.  Only the first ``experts`` columns of ``logits`` are the router's."""
+        z = logits[:, :experts if experts is not None else logits.shape[1]].to(self.cd)
+        if scoring == "chosen":
+            val, idx = torch.sort(z, dim=-1, descending=True, stable=True)
+            ids.copy_(idx[:, :top].to(ids.dtype))
+            gates.copy_(torch.softmax(val[:, :top], dim=-1).to(gates.dtype))
+            return
+        score = torch.softmax(z, dim=-1)
+        masked = score.clone()
+        if groups is not None and groups[1] < groups[0]:
+            count, keep = groups
+            n, E = score.shape
+            best = score.view(n, count, E // count).max(dim=-1).values
+            order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
+            allowed = torch.zeros(n, count, dtype=torch.bool)
+            allowed.scatter_(1, order, True)
+            masked[~allowed.repeat_interleave(E // count, dim=1)] = -1.0
+        idx = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :top]
+        ids.copy_(idx.to(ids.dtype))
+        gates.copy_((torch.gather(score, 1, idx) * weight_scale).to(gates.dtype))
 
-    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos):
+    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos, experts=None, scoring="chosen", groups=None,
+                       weight_scale=1.0):
         """moe_route, then moe_plan."""
-        self.moe_route(logits, top, ids, gates)
-        self.moe_plan(ids, logits.shape[1], offsets, perm, pos)
+        self.moe_route(logits, top, ids, gates, experts=experts, scoring=scoring, groups=groups, weight_scale=weight_scale)
+        self.moe_plan(ids, experts if experts is not None else logits.shape[1], offsets, perm, pos)
 
     def moe_plan(self, ids, num_experts, offsets, perm, pos):
         """The pairs (token, choice), numbered token * top + choice, listed by expert in ascending pair number:
@@ -519,13 +538,139 @@ class ReferenceKernels:
                 raise ValueError(epilogue)
             out[a:b] = y.to(out.dtype)
 
-    def moe_combine(self, y, pos, gates, out):
-        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending."""
+    def moe_combine(self, y, pos, gates, out, shared=None, shared_logit=None):
+        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending; + shared[n] (times sigmoid(shared_logit[n]))."""
         n, top = gates.shape
         acc = torch.zeros(n, y.shape[1], dtype=self.cd)
         for j in range(top):
             acc = acc + gates[:, j].to(self.cd)[:, None] * y[pos.view(n, top)[:, j].long()].to(self.cd)
+        if shared is not None:
+            g = torch.sigmoid(shared_logit.to(self.cd))[:, None] if shared_logit is not None else 1.0
+            acc = acc + g * shared.to(self.cd)
         out.copy_(acc.to(out.dtype))
+
+    # ------------------------------------------------------------------ decoders with latent attention
+    def _group_norm(self, v, weight, groups, eps):
+        n, W = v.shape
+        p = v.to(self.cd).view(n, groups, W // groups)
+        p = p * torch.rsqrt(p.pow(2).mean(-1, keepdim=True) + eps)
+        return p.reshape(n, W) * weight.to(self.cd)
+
+    def group_rmsnorm(self, x, weight, groups, eps, out, delta=None, mult=1.0, rows=None, keep=None):
+        """x += mult * delta (in place unless ``rows``); keep = the updated rows; out = the norm in groups of them."""
+        if rows is None:
+            if delta is not None:
+                x.add_(mult * delta.to(torch.float32))
+            src = x
+        else:
+            src = x[rows.long()]
+            if delta is not None:
+                src = src + mult * delta[rows.long()].to(torch.float32)
+        if keep is not None:
+            keep.copy_(src)
+        out.copy_(self._group_norm(src, weight, groups, eps).to(out.dtype))
+
+    def depth_average(self, x, delta, mult, hist, depth, coeff, out=None, next_weight=None, groups=1, eps=0.0):
+        """hist[:, depth] = x + mult * delta; x = sum_(j <= depth) coeff[j] * hist[:, j]; out = the next norm of x."""
+        v = x if delta is None else x + mult * delta.to(torch.float32)
+        hist[:, depth] = v
+        x.copy_((hist[:, :depth + 1].to(self.cd) * coeff.to(self.cd)[None, :, None]).sum(1).to(torch.float32))
+        if out is not None:
+            out.copy_(self._group_norm(x, next_weight, groups, eps).to(out.dtype))
+
+    def causal_conv(self, h, weight, state, state_slots, cu_q, seq_lens, req_index, out):
+        """out_t = h_t + sum_j weight[:, j] * h_(t - taps + 1 + j) per request; state[slot] holds the taps - 1 inputs before
+        the portion (oldest first) and takes the portion's last inputs."""
+        taps = weight.shape[1]
+        K = taps - 1
+        w = weight.to(self.cd)
+        for r in range(cu_q.numel() - 1):
+            a, b = int(cu_q[r]), int(cu_q[r + 1])
+            if int(seq_lens[r]) <= 0 or a == b:
+                out[a:b] = h[a:b]
+                continue
+            slot = int(state_slots[r])
+            seq = torch.cat((state[slot, :K].to(self.cd), h[a:b].to(self.cd)), dim=0)        # inputs -K .. len - 1
+            y = h[a:b].to(self.cd).clone()
+            for j in range(taps):
+                y = y + w[:, j] * seq[j:j + (b - a)]
+            out[a:b] = y.to(out.dtype)
+            if K:
+                state[slot, :K] = seq[seq.shape[0] - K:].to(state.dtype)
+
+    def latent_prepare(self, proj, heads, dim, rot, rank, down_col, norm_weight, eps, table, dims, q_plain, q_rot, latent_pages,
+                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0):
+        """Queries head-major, rotated parts turned, the normalised latent and the turned shared key part into the pages."""
+        n = proj.shape[0]
+        seg = q_plain.shape[1]
+        p = proj.to(self.cd)
+        q = p[:, :heads * (dim + rot)].view(n, heads, dim + rot)
+        q_plain[:, :n] = q[..., :dim].transpose(0, 1).to(q_plain.dtype)
+        offsets.copy_(torch.arange(heads + 1, dtype=offsets.dtype) * seg)
+        if tile_head is not None:
+            tile_head.copy_((torch.arange(tile_head.numel()) // (seg // tile)).to(tile_head.dtype))
+
+        def turn(v):                     # v [n, ..., rot]
+            if table is None:
+                return v
+            cs = table.to(self.cd).view(n, dims // 2, 2)
+            while cs.dim() < v.dim() + 1:
+                cs = cs.unsqueeze(1)
+            c, s = cs[..., 0], cs[..., 1]
+            a, b = v[..., :dims // 2], v[..., dims // 2:dims]
+            return torch.cat((a * c - b * s, b * c + a * s, v[..., dims:]), dim=-1)
+
+        if rot:
+            q_rot.copy_(turn(q[..., dim:]).to(q_rot.dtype))
+        if slot_mapping is None:
+            return
+        lat = p[:, down_col:down_col + rank]
+        lat = lat * torch.rsqrt(lat.pow(2).mean(-1, keepdim=True) + eps) * norm_weight.to(self.cd)
+        slots = slot_mapping[:n].long()
+        live = slots >= 0
+        latent_pages.view(-1, rank)[slots[live]] = lat[live].to(latent_pages.dtype)
+        if rot:
+            kr = turn(p[:, down_col + rank:down_col + rank + rot])
+            rot_pages.view(-1, rot)[slots[live]] = kr[live].to(rot_pages.dtype)
+
+    def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
+                         window, tokens):
+        """Every head of a token attends over its request's cached latents (and the shared rotated key part)."""
+        heads, seg, rank = q_lat.shape
+        ps = latent_pages.shape[2]
+        lat = latent_pages.view(-1, rank)
+        rk = rot_pages.view(-1, rot_pages.shape[3]) if rot_pages is not None else None
+        for r in range(cu_q.numel() - 1):
+            a, b, L = int(cu_q[r]), int(cu_q[r + 1]), int(seq_lens[r])
+            for t in range(a, b):
+                if L <= 0:
+                    out[:, t] = 0
+                    continue
+                p = L - (b - a) + (t - a)
+                first = max(0, p - window + 1) if window else 0
+                js = torch.arange(first, p + 1)
+                slots = block_tables[r][(js // ps).long()].long() * ps + js % ps
+                c = lat[slots].to(self.cd)                                             # [keys, rank]
+                s = q_lat[:, t].to(self.cd) @ c.t()                                    # [heads, keys]
+                if rk is not None:
+                    s = s + q_rot[t].to(self.cd) @ rk[slots].to(self.cd).t()
+                s = s * scale
+                m = s.max(dim=1).values
+                if sink is not None:
+                    m = torch.maximum(m, sink.to(self.cd))
+                e = torch.exp(s - m[:, None])
+                den = e.sum(1)
+                if sink is not None:
+                    den = den + torch.exp(sink.to(self.cd) - m)
+                out[:, t] = ((e / den[:, None]) @ c).to(out.dtype)
+
+    def gate_heads(self, y, gate, out, tokens):
+        """out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v])."""
+        heads, seg, vdim = y.shape
+        v = y[:, :tokens].to(self.cd).transpose(0, 1).reshape(tokens, heads * vdim)
+        if gate is not None:
+            v = v * torch.sigmoid(gate.to(self.cd))
+        out.copy_(v.to(out.dtype))
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):
