@@ -149,3 +149,15 @@ def forward(cfg, weights, tokens, return_layers=False):
         after.append(x)
     logits = group_rms_norm(x, w64(weights, "final.norm"), groups, eps) @ w64(weights, "head").T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def greedy(cfg, weights, prompt, n):
+    """The ``n`` tokens that follow ``prompt`` when the largest logit is always taken (the lowest index among equals);
+    every token is computed from the whole sequence again."""
+    toks = list(prompt)
+    out = []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(cfg, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out

@@ -45,10 +45,10 @@ TINY = {
     # all three mixers, a layer without feed-forward, three norm groups, three taps, groups of experts of which two of three
     # are kept, a shared expert in one layer only, float32 storage
     "F1": dict(config=_config(101, 48, 1e-5, 3, 0.5, 3, [
-        _rot(3, 8, 6, 10, 12, 0.4, 100.0, _moe(6, 2, 20, groups=(3, 2), scale=1.5, shared=28)),
+        _rot(3, 8, 6, 10, 12, 0.4, 100.0, _moe(6, 3, 20, groups=(3, 2), scale=1.5, shared=28)),
         _win(2, 12, 8, 16, 0.35, 7, None),
         _win(4, 4, 4, 8, 0.6, 20, _moe(4, 4, 12), plain=True),
-        _rot(2, 6, 2, 6, 10, 0.5, 7.0, _moe(4, 1, 16, groups=(4, 1), scale=2.5, shared=8))]),
+        _rot(2, 6, 2, 6, 10, 0.5, 7.0, _moe(4, 2, 16, groups=(2, 1), scale=2.5, shared=8))]),
                page_size=16, store="float32", seed=21),
     # values that make mechanisms coincide or vanish: one norm group, one tap (no state to carry), a multiplier of one, a
     # window of one token and one longer than any test sequence, one expert group, top 1, pages of 8; bfloat16 storage
@@ -90,7 +90,7 @@ def make_weights(cfg, seed, sharpen=3.0):
         w[p + "mix.dkv.norm"] = near_one(R)
         w[p + "mix.uk"], w[p + "mix.uv"], w[p + "mix.o"] = mat(H * D, R, 1.5), mat(H * Vd, R), mat(W, H * Vd)
         if layer["type"] != "latent_attention_3":
-            w[p + "mix.sink"] = 1.5 * torch.randn(H, generator=g)
+            w[p + "mix.sink"] = 1.5 + 2.0 * torch.randn(H, generator=g)
             w[p + "mix.g"] = mat(H * Vd, W, 2.0)
         mlp = layer["mlp"]
         if mlp is not None:
