@@ -631,6 +631,32 @@ def hybrid_config(size):
             "token_side": {"dim": 32}, "logit_softcap": 30.0}
 
 
+def latent_config(size):
+    """A Filorax config.json mapping at the width, depth, head count and ACTIVE parameter count of hybrid_config(size):
+    layers rotated-causal, window + sink + gate, window + ordinary softmax, rotated-causal, ...; heads of the attention's
+    size with a latent of twice and a rotated part of a quarter of it; 8 experts in 4 groups of which 2 are kept and 2
+    experts run, each a sixth of the dense feed-forward's width, beside a shared expert of a third (together the two
+    thirds that run in hybrid_config); four taps, two norm groups."""
+    W, layers, H, _, d, _, _, _, ff, window = {
+        "s": (1024, 8, 16, 4, 64, 8, 64, 128, 3072, 512),
+        "m": (2048, 8, 16, 4, 128, 16, 64, 128, 6144, 1024),
+        "l": (4096, 8, 32, 8, 128, 32, 64, 128, 12288, 1024),
+    }[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff // 3},
+           "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    entries = []
+    for i in range(layers):
+        mixer = {"heads": H, "dim": d, "vdim": d, "kv_rank": 2 * d, "scale": (d + (d // 4 if i % 4 in (0, 3) else 0)) ** -0.5}
+        if i % 4 in (0, 3):
+            mixer.update(rot_dim=d // 4, rot={"base": 1e6, "dims": d // 4})
+            entries.append({"type": "latent_attention_2", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer.update(mask={"size": window})
+            entries.append({"type": "latent_attention" if i % 4 == 1 else "latent_attention_3", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Filorax", "canon": {"taps": 4}, "layers": entries, "norm": {"eps": 1e-6, "groups": 2},
+            "residual_mult": 0.5, "vocab": 32768, "width": W}
+
+
 def attention_shape(conf):
     """(key/value heads, head size, chunk or None) of a design's attention layers, from its config.json mapping."""
     if "layers" not in conf:
@@ -641,6 +667,8 @@ def attention_shape(conf):
             return m["kv_heads"], m["dim"], (m.get("mask") or {}).get("size")
         if layer["type"] == "parallel":
             return m["left"]["kv_heads"], m["left"]["dim"], None
+        if layer["type"].startswith("latent_attention"):
+            return 1, m["kv_rank"] // 2, None              # a latent of kv_rank entries stands for a key and a value
     return 1, 1, None
 
 
@@ -652,11 +680,15 @@ class DesignTimer(KernelClassTimer):
                                           "attention_talk", "residual_norm_update", "add_rows", "scaled_sum", "token_side_gate",
                                           "softcap", "token_shift_mix", "linear_scan", "gated_unit_scan", "rotary_store",
                                           "rotate_rows", "paged_attention_streams", "moe_route", "moe_plan", "moe_linear",
-                                          "moe_combine", "moe_plan_padded", "moe_gather", "moe_linear_grouped")
+                                          "moe_combine", "moe_plan_padded", "moe_gather", "moe_linear_grouped", "moe_route_plan",
+                                          "group_rmsnorm", "depth_average", "causal_conv", "latent_prepare", "latent_attention",
+                                          "gate_heads")
 
-    def __init__(self, kernels, vocab, pairs, key_bytes):
+    def __init__(self, kernels, vocab, pairs, key_bytes, positions=(), head_weights=()):
         super().__init__(kernels, vocab)
         self.pairs, self.key_bytes = pairs, key_bytes
+        self.positions = list(positions)           # the step's query positions (latent attention: a window per layer)
+        self.head_weights = set(head_weights)      # data pointers of per-head matrices that run as grouped products
         self.work = []            # per record: (tensor flops, float32 flops, bytes)
 
     def _classify(self, name, a, kw):
@@ -682,6 +714,19 @@ class DesignTimer(KernelClassTimer):
         elif name == "gated_unit_scan":
             proj, out = a[0], a[7]
             cls, ff, by = "recurrence", 10 * out.numel(), proj.numel() * 4 + out.numel() * out.element_size()
+        elif name == "latent_attention":
+            q_lat, lat_pages, rot_pages, window = a[0], a[2], a[3], a[11]
+            H, _, R = q_lat.shape
+            r = rot_pages.shape[3] if rot_pages is not None else 0
+            seen = [min(p + 1, window) if window else p + 1 for p in self.positions]
+            # the least: scores and sums over the latent itself (keys and values are never formed); every latent a query of the
+            # step sees is read once
+            span = max(seen) + len(seen) - 1 if len(set(self.positions)) > 1 else sum(seen)
+            cls, tf, by = "attention", H * (4 * R + 2 * r) * sum(seen), span * (R + r) * lat_pages.element_size()
+        elif name in ("moe_linear", "moe_linear_grouped") and a[1].data_ptr() in self.head_weights:
+            w, out = a[1], a[5] if name == "moe_linear" else a[3]
+            rows = len(self.positions) * w.shape[0]
+            cls, tf, by = "head products", 2 * rows * w.shape[1] * w.shape[2], w.numel() * w.element_size()
         elif name == "moe_linear":
             x, w, out = a[0], a[1], a[5]
             experts = min(w.shape[0], out.shape[0])           # experts whose matrices a step has to read at the least
@@ -746,6 +791,8 @@ def run_designs(args):
     for size in args.design_sizes.split(","):
         kaf, qwen = design_configs(size)
         pair = (("lunelorn", hybrid_config(size)), ("kafunex", kaf)) if args.hybrid else (("kafunex", kaf), ("qwen3", qwen))
+        if args.latent:
+            pair = (("filorax", latent_config(size)), ("lunelorn", hybrid_config(size)))
         for design, conf in pair:
             pool = batch * (context + 64) + PREFILL_TOKENS + 64
             opts = EngineOptions(dtype="bfloat16", page_size=16, num_pages=pool // 16, max_num_seqs=batch,
@@ -767,9 +814,12 @@ def run_designs(args):
             # where the time goes: an eager pass with events around every launch
             K = runner.rt.kernels
             graphs, runner.use_graphs = runner.use_graphs, False
+            mixers = [getattr(layer, "mixer", None) for layer in runner.model.layers]
+            heads_w = [w.data_ptr() for m in mixers for w in (getattr(m, "w_absorb", None), getattr(m, "w_values", None)) if w is not None]
             toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(2)).tolist()
             runner.cache.add_request("kp")
-            with DesignTimer(K, vocab, visible_pairs(chunk, range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2) as t:
+            with DesignTimer(K, vocab, visible_pairs(chunk, range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2,
+                             positions=range(PREFILL_TOKENS), head_weights=heads_w) as t:
                 torch.cuda.synchronize()
                 hold_the_device(20.0)
                 runner.step([StepEntry("kp", toks, [PREFILL_TOKENS - 1])])
@@ -780,7 +830,8 @@ def run_designs(args):
             step = lambda: runner.step_and_sample([StepEntry(x, [1], [0]) for x in rids], zeros, zeros)      # noqa: E731
             step()
             seen = visible_pairs(chunk, [context + 1])          # keys a decoded token sees
-            with DesignTimer(K, vocab, batch * seen, batch * seen * G_ * d_ * 2 * 2) as t:
+            with DesignTimer(K, vocab, batch * seen, batch * seen * G_ * d_ * 2 * 2, positions=[context + 1] * batch,
+                             head_weights=heads_w) as t:
                 for _ in range(3):
                     torch.cuda.synchronize()
                     hold_the_device()
@@ -979,6 +1030,8 @@ def main():
                     help="instead of the default workload: the Kafunex design beside Qwen3 at equal sizes (prefill and decode)")
     ap.add_argument("--hybrid", action="store_true",
                     help="with --designs: the Lunelorn design beside Kafunex (equal width, depth and active parameters)")
+    ap.add_argument("--latent", action="store_true",
+                    help="with --designs: the Filorax design beside Lunelorn (equal width, depth and active parameters)")
     ap.add_argument("--design-sizes", default="s,m", help="with --designs: which of the sizes s, m, l (commas between)")
     ap.add_argument("--kernels-alone", action="store_true",
                     help="with --designs: only the talking attention and the gated recurrence, each alone (a small case)")
