@@ -1,0 +1,317 @@
+// Attention over cached latents on tensor cores (bfloat16 operands, float32 scores, softmax and sums), the absorbed form of
+// attention_latent.cu: every head of a token attends over the same rows [latent | rotated key part], so the (token, head)
+// pairs of a request are the rows of one product against those rows, and the weighted sum is taken over the latent itself.
+//
+// A CTA takes 64 consecutive rows rho = (token - first token of the step) * heads + head of one request (16 per warp) and
+// walks the keys they see in tiles of 64, two tiles in flight (16-byte cp.async, rows padded by 16 bytes so that ldmatrix
+// meets no bank conflict).  Scores S = Q K^T by mma.sync m16n8k16 over the latent's and the rotated part's columns; mask
+// (causal, window), running maximum and sum in the base-2 domain; the weights, rounded to bfloat16, are the left operand
+// of O += P C over the latent's columns, which the same shared-memory rows give through ldmatrix.trans.  A sink starts a
+// row's maximum at the sink and its sum at 1.  With `splits` > 1 (few rows and a long context: decode) the keys of a CTA's
+// rows are divided among that many CTAs, which write unnormalised sums with their maximum and denominator, and a second
+// kernel merges them (the sink joins there).
+#include "common.cuh"
+#include <math.h>
+
+typedef __nv_bfloat16 bf16;
+constexpr int LM_ROWS = 64, LM_KEYS = 64, LM_THREADS = 128;
+
+__device__ __forceinline__ uint32_t lm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lm_cp16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;                   // 0: zeros are written and src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(lm_smem(dst)), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void lm_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void lm_ldm(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(lm_smem(p)));
+}
+__device__ __forceinline__ void lm_ldm_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(lm_smem(p)));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+constexpr float LM_LOG2E = 1.4426950408889634f;
+
+// Scratch of the split form, per (request, row tile, split): 64 rows of RANK sums, then 64 maxima, then 64 denominators.
+__host__ __device__ inline size_t lm_part_floats(int rank_pad) { return (size_t)LM_ROWS * (rank_pad + 2); }
+
+template <int RANK>          // columns of the latent in shared memory (the latent's width rounded up; the rest zeros)
+__global__ void __launch_bounds__(LM_THREADS)
+latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, int seg, const bf16* __restrict__ lat_pages,
+                            const bf16* __restrict__ rot_pages, const int* __restrict__ block_tables, int table_stride, int page_size,
+                            const int* __restrict__ cu_q, const int* __restrict__ seq_lens, const void* __restrict__ sink, int stype,
+                            bf16* __restrict__ out, float* __restrict__ part, int heads, int rank, int rot, int rot_pad,
+                            float scale, int window, int splits) {
+  extern __shared__ __align__(16) unsigned char lm_raw[];
+  const int KD = RANK + rot_pad, LD = KD + 8;      // columns of a row, and its length in shared memory
+  bf16* Qs = reinterpret_cast<bf16*>(lm_raw);
+  bf16* Ks = Qs + (size_t)LM_ROWS * LD;            // two stages of LM_KEYS rows
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int r = blockIdx.y, split = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q0 = cu_q[r], nq = cu_q[r + 1] - q0, L = seq_lens[r];
+  const int nrows = nq * heads, row0 = blockIdx.x * LM_ROWS;
+  if (row0 >= nrows) return;
+  if (L <= 0) {                                    // a padding request of a recorded step: zeros
+    if (split == 0)
+      for (int i = tid; i < min(LM_ROWS, nrows - row0) * rank; i += LM_THREADS) {
+        const int rho = row0 + i / rank;
+        out[((size_t)(rho % heads) * seg + q0 + rho / heads) * rank + i % rank] = __float2bfloat16(0.f);
+      }
+    return;                                        // (the merge kernel skips such a request by its length)
+  }
+  const int p_first = L - nq;
+  const int p_lo = p_first + row0 / heads, p_hi = p_first + min(nrows - 1, row0 + LM_ROWS - 1) / heads;
+  const int k_lo = window > 0 ? max(0, p_lo - window + 1) : 0;
+  int kb = k_lo, ke = p_hi;
+  if (splits > 1) {
+    const int per = ((p_hi - k_lo + splits) / splits + LM_KEYS - 1) / LM_KEYS * LM_KEYS;
+    kb = k_lo + split * per;
+    ke = min(p_hi, kb + per - 1);
+  }
+  float* my_part = part ? part + ((size_t)(r * gridDim.x + blockIdx.x) * splits + split) * lm_part_floats(RANK) : nullptr;
+  // ---- the rows' queries: [latent-space part | rotated part], bfloat16
+  for (int i = tid; i < LM_ROWS * (KD / 2); i += LM_THREADS) {
+    const int row = i / (KD / 2), c = (i - row * (KD / 2)) * 2, rho = row0 + row;
+    float a = 0.f, b = 0.f;
+    if (rho < nrows) {
+      const int t = q0 + rho / heads, h = rho % heads;
+      if (c < rank) {
+        const float2 v = *reinterpret_cast<const float2*>(q_lat + ((size_t)h * seg + t) * rank + c);
+        a = v.x; b = v.y;
+      } else if (c >= RANK && c - RANK < rot) {
+        const float2 v = *reinterpret_cast<const float2*>(q_rot + ((size_t)t * heads + h) * rot + (c - RANK));
+        a = v.x; b = v.y;
+      }
+    }
+    *reinterpret_cast<uint32_t*>(Qs + (size_t)row * LD + c) = lm_pack(a, b);
+  }
+  const int* table = block_tables + (size_t)r * table_stride;
+  const int chunks = KD / 8;                       // 16-byte pieces of a row
+  auto load_tile = [&](int tile0, int stage) {
+    bf16* dst = Ks + (size_t)stage * LM_KEYS * LD;
+    for (int i = tid; i < LM_KEYS * chunks; i += LM_THREADS) {
+      const int key = i / chunks, c = (i - key * chunks) * 8, j = tile0 + key;
+      const bool live = j >= kb && j <= ke;
+      const bf16* src = lat_pages;
+      bool valid = false;
+      if (live) {
+        const size_t slot = (size_t)table[j / page_size] * page_size + j % page_size;
+        if (c < rank) { src = lat_pages + slot * rank + c; valid = true; }
+        else if (c >= RANK && c - RANK < rot) { src = rot_pages + slot * rot + (c - RANK); valid = true; }
+      }
+      lm_cp16(dst + (size_t)key * LD + c, src, valid);
+    }
+  };
+  float o[RANK / 8][4];
+#pragma unroll
+  for (int n = 0; n < RANK / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  // per thread two rows: lane / 4 and lane / 4 + 8 of the warp's sixteen
+  const int rowA = row0 + warp * 16 + (lane >> 2), rowB = rowA + 8;
+  const int pA = rowA < nrows ? p_first + rowA / heads : -1, pB = rowB < nrows ? p_first + rowB / heads : -1;
+  const int loA = window > 0 ? pA - window + 1 : 0, loB = window > 0 ? pB - window + 1 : 0;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  if (sink != nullptr && splits == 1) {
+    // the four lanes that share a row hold parts of its sum: the sink's 1 stands on one of them
+    if (pA >= 0) { mA = load_as_f32(sink, stype, rowA % heads) * LM_LOG2E; lA = (lane & 3) == 0 ? 1.f : 0.f; }
+    if (pB >= 0) { mB = load_as_f32(sink, stype, rowB % heads) * LM_LOG2E; lB = (lane & 3) == 0 ? 1.f : 0.f; }
+  }
+  const bool warp_live = row0 + warp * 16 < nrows;
+  const float sc = scale * LM_LOG2E;
+  const int ntiles = ke >= kb ? (ke - kb) / LM_KEYS + 1 : 0;
+  if (ntiles > 0) load_tile(kb, 0);
+  lm_commit();
+  for (int it = 0; it < ntiles; ++it) {
+    if (it + 1 < ntiles) load_tile(kb + (it + 1) * LM_KEYS, (it + 1) & 1);
+    lm_commit();
+    lm_wait<1>();
+    __syncthreads();
+    const int tile0 = kb + it * LM_KEYS;
+    const bf16* Kt = Ks + (size_t)(it & 1) * LM_KEYS * LD;
+    // rows of this warp that see nothing of the tile skip it (the tile lies after them, or before their window)
+    const int w_hi = p_first + min(nrows - 1, row0 + warp * 16 + 15) / heads, w_lo_row = p_first + (row0 + warp * 16) / heads;
+    const bool useful = warp_live && tile0 <= w_hi && (window == 0 || tile0 + LM_KEYS - 1 > w_lo_row - window);
+    if (useful) {
+      float s[LM_KEYS / 8][4];
+#pragma unroll
+      for (int n = 0; n < LM_KEYS / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int kk = 0; kk < KD / 16; ++kk) {
+        uint32_t a[4];
+        lm_ldm(a, Qs + (size_t)(warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int np = 0; np < LM_KEYS / 16; ++np) {
+          uint32_t b[4];
+          lm_ldm(b, Kt + (size_t)(np * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+          lm_mma(s[2 * np], a, b[0], b[1]);
+          lm_mma(s[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+      float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < LM_KEYS / 8; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = tile0 + n * 8 + (lane & 3) * 2 + (c & 1);
+          const bool second = c >= 2;
+          const int p = second ? pB : pA, lo = second ? loB : loA;
+          const bool see = key <= p && key >= lo && key >= kb && key <= ke;
+          const float v = see ? s[n][c] * sc : -INFINITY;
+          s[n][c] = v;
+          if (second) mxB = fmaxf(mxB, v); else mxA = fmaxf(mxA, v);
+        }
+      }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+      const float baseA = nA == -INFINITY ? 0.f : nA, baseB = nB == -INFINITY ? 0.f : nB;      // a row that has seen nothing yet
+      const float cA = exp2f(mA - baseA), cB = exp2f(mB - baseB);
+      mA = nA; mB = nB;
+      float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+      for (int n = 0; n < LM_KEYS / 8; ++n) {
+        s[n][0] = exp2f(s[n][0] - baseA); s[n][1] = exp2f(s[n][1] - baseA);
+        s[n][2] = exp2f(s[n][2] - baseB); s[n][3] = exp2f(s[n][3] - baseB);
+        sumA += s[n][0] + s[n][1];
+        sumB += s[n][2] + s[n][3];
+      }
+      lA = fmaf(lA, cA, sumA);
+      lB = fmaf(lB, cB, sumB);
+#pragma unroll
+      for (int n = 0; n < RANK / 8; ++n) { o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB; }
+#pragma unroll
+      for (int ks = 0; ks < LM_KEYS / 16; ++ks) {
+        uint32_t a[4] = {lm_pack(s[2 * ks][0], s[2 * ks][1]), lm_pack(s[2 * ks][2], s[2 * ks][3]),
+                         lm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), lm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+#pragma unroll
+        for (int np = 0; np < RANK / 16; ++np) {
+          uint32_t b[4];
+          lm_ldm_t(b, Kt + (size_t)(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + np * 16 + (lane >> 4) * 8);
+          lm_mma(o[2 * np], a, b[0], b[1]);
+          lm_mma(o[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();                               // the stage is free for the load after next
+  }
+  lm_wait<0>();
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int rho = half ? rowB : rowA;
+    if (rho >= nrows) continue;
+    const float l = half ? lB : lA, m = half ? mB : mA;
+    if (splits == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = out + ((size_t)(rho % heads) * seg + q0 + rho / heads) * rank;
+#pragma unroll
+      for (int n = 0; n < RANK / 8; ++n) {
+        const int c = n * 8 + (lane & 3) * 2;
+        if (c < rank) *reinterpret_cast<uint32_t*>(dst + c) = lm_pack(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+      }
+    } else {
+      const int row = rho - row0;
+      float* dst = my_part + (size_t)row * RANK;
+#pragma unroll
+      for (int n = 0; n < RANK / 8; ++n) {
+        const int c = n * 8 + (lane & 3) * 2;
+        *reinterpret_cast<float2*>(dst + c) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+      }
+      if ((lane & 3) == 0) {
+        my_part[(size_t)LM_ROWS * RANK + row] = m;
+        my_part[(size_t)LM_ROWS * RANK + LM_ROWS + row] = l;
+      }
+    }
+  }
+}
+
+// The split form's second step: per row the maximum over the splits (and the sink), the denominators and sums brought to
+// it, and the quotient.  A warp per row.
+template <int RANK>
+__global__ void __launch_bounds__(LM_THREADS)
+latent_attention_merge_kernel(const float* __restrict__ part, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                              const void* __restrict__ sink, int stype, bf16* __restrict__ out, int seg, int heads, int rank,
+                              int splits) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = cu_q[r], nrows = (cu_q[r + 1] - q0) * heads, row0 = blockIdx.x * LM_ROWS;
+  if (row0 >= nrows || seq_lens[r] <= 0) return;
+  const size_t PF = lm_part_floats(RANK);
+  const float* base = part + (size_t)(r * gridDim.x + blockIdx.x) * splits * PF;
+  for (int row = warp; row < min(LM_ROWS, nrows - row0); row += LM_THREADS / 32) {
+    const int rho = row0 + row, h = rho % heads;
+    const float s2 = sink != nullptr ? load_as_f32(sink, stype, h) * LM_LOG2E : -INFINITY;
+    float m = s2;
+    for (int z = 0; z < splits; ++z) m = fmaxf(m, base[z * PF + (size_t)LM_ROWS * RANK + row]);
+    float l = sink != nullptr ? exp2f(s2 - m) : 0.f;
+    for (int z = 0; z < splits; ++z)
+      l = fmaf(base[z * PF + (size_t)LM_ROWS * RANK + LM_ROWS + row], exp2f(base[z * PF + (size_t)LM_ROWS * RANK + row] - m), l);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    bf16* dst = out + ((size_t)h * seg + q0 + rho / heads) * rank;
+    for (int c = lane; c < rank; c += 32) {
+      float acc = 0.f;
+      for (int z = 0; z < splits; ++z)
+        acc = fmaf(base[z * PF + (size_t)row * RANK + c], exp2f(base[z * PF + (size_t)LM_ROWS * RANK + row] - m), acc);
+      dst[c] = __float2bfloat16(acc * inv);
+    }
+  }
+}
+
+static int lm_rank_pad(int rank) { return rank <= 32 ? 32 : rank <= 64 ? 64 : rank <= 128 ? 128 : 256; }
+
+// Floats of scratch that `splits` > 1 needs for a step of `requests` requests of at most `max_q_len` tokens.
+IFB_EXPORT long long ifb_latent_attention_mma_scratch_floats(int requests, int max_q_len, int heads, int rank, int splits) {
+  if (splits <= 1) return 0;
+  const long long tiles = ((long long)max_q_len * heads + LM_ROWS - 1) / LM_ROWS;
+  return (long long)requests * tiles * splits * (long long)lm_part_floats(lm_rank_pad(rank));
+}
+
+template <int RANK>
+static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void* lat_pages, const void* rot_pages, const int* block_tables,
+                     int table_stride, int page_size, const int* cu_q, const int* seq_lens, const void* sink, int stype, void* out,
+                     float* part, int requests, int max_q_len, int heads, int rank, int rot, float scale, int window, int splits,
+                     cudaStream_t stream) {
+  const int rot_pad = (rot + 15) / 16 * 16, LD = RANK + rot_pad + 8;
+  const size_t smem = (size_t)(LM_ROWS + 2 * LM_KEYS) * LD * sizeof(bf16);
+  if (smem > 220 * 1024) return IFB_ERR_SIZE;
+  IFB_ALLOW_SMEM(latent_attention_mma_kernel<RANK>, smem);
+  const dim3 grid((unsigned)(((long long)max_q_len * heads + LM_ROWS - 1) / LM_ROWS), (unsigned)requests, (unsigned)splits);
+  int rc = ifb_launch(latent_attention_mma_kernel<RANK>, grid, dim3(LM_THREADS), smem, stream, q_lat, q_rot, seg, (const bf16*)lat_pages,
+                      (const bf16*)rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, (bf16*)out, part, heads,
+                      rank, rot, rot_pad, scale, window, splits);
+  if (rc != IFB_OK || splits <= 1) return rc;
+  return ifb_launch(latent_attention_merge_kernel<RANK>, dim3(grid.x, grid.y), dim3(LM_THREADS), 0, stream, (const float*)part, cu_q,
+                    seq_lens, sink, stype, (bf16*)out, seg, heads, rank, splits);
+}
+
+// bfloat16 pages and outputs; rank and rot multiples of 8, rank at most 256.
+IFB_EXPORT int ifb_latent_attention_mma(const float* q_lat, const float* q_rot, int seg, const void* lat_pages, const void* rot_pages,
+                                        const int* block_tables, int table_stride, int page_size, const int* cu_q, const int* seq_lens,
+                                        const void* sink, int stype, void* out, float* part, int requests, int max_q_len, int heads,
+                                        int rank, int rot, float scale, int window, int splits, cudaStream_t stream) {
+  if (requests <= 0 || max_q_len <= 0) return IFB_OK;
+  if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 ||
+      (splits > 1 && part == nullptr))
+    return IFB_ERR_SIZE;
+#define LM_CASE(P)                                                                                                             \
+  return lm_launch<P>(q_lat, q_rot, seg, lat_pages, rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, \
+                      out, part, requests, max_q_len, heads, rank, rot, scale, window, splits, stream)
+  switch (lm_rank_pad(rank)) {
+    case 32: LM_CASE(32);
+    case 64: LM_CASE(64);
+    case 128: LM_CASE(128);
+    default: LM_CASE(256);
+  }
+#undef LM_CASE
+}

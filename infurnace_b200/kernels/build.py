@@ -41,8 +41,8 @@ LIBRARIES: Dict[str, tuple] = {
     # page streams, routed experts
     "hybrid": (["sandwich.cu", "linear_scan.cu", "attention_streams.cu", "moe.cu"], []),
     # decoders with latent attention: norms in groups, the short causal convolution, the average over depth, the
-    # preparation of queries and latents, attention over cached latents, the output gate
-    "latent": (["latent.cu", "attention_latent.cu"], []),
+    # preparation of queries and latents, attention over cached latents (plain and on tensor cores), the output gate
+    "latent": (["latent.cu", "attention_latent.cu", "attention_latent_mma.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }

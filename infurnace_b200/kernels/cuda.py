@@ -148,6 +148,7 @@ class CudaKernels:
         self._attn_mma = {}        # head size -> library
         self._attn_scratch = None
         self._attn_counters = None
+        self.latent_mma_calls = 0      # steps of the latent attention that ran on tensor cores
         self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self.attention_scratch_cap = 64 << 20     # bytes of split scratch beyond which a step runs unsplit
         c.ifb_paged_attention_simt.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -1304,6 +1305,11 @@ class CudaKernels:
             m.ifb_latent_attention.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                c_float, c_int, c_void_p]
+            m.ifb_latent_attention_mma.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                   c_float, c_int, c_int, c_void_p]
+            m.ifb_latent_attention_mma_scratch_floats.restype = c_longlong
+            m.ifb_latent_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         return self._lat
 
     def group_rmsnorm(self, x, weight, groups, eps, out, delta=None, mult=1.0, rows=None, keep=None):
@@ -1392,10 +1398,16 @@ class CudaKernels:
                                                   self._stream()), "latent_prepare")
 
     def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
-                         window, tokens):
+                         window, tokens, max_q_len=None, max_seq_len=None, exact=False):
         """Attention of every head over the request's cached latents (the absorbed form): q_lat [heads, seg, rank] float32,
         q_rot [n, heads, rot] float32 (None without a rotated part), out [heads, seg, rank] = the softmax-weighted sum of
-        latents per head.  ``sink`` [heads]: exp of it joins the denominator.  ``window`` 0: every earlier position."""
+        latents per head.  ``sink`` [heads]: exp of it joins the denominator.  ``window`` 0: every earlier position.
+
+        bfloat16 pages with a latent of at most 256 entries (latent and rotated part multiples of 8), when the caller gives
+        the step's longest portion and context: the tensor-core kernel (csrc/attention_latent_mma.cu; float32 scores,
+        softmax and sums, the weights rounded to bfloat16 as the left operand of the weighted sum), the context divided
+        among several CTAs where a step has few rows.  float32, other sizes and ``exact``: the plain kernel, a warp per
+        (token, head), which keeps float32 weights through the sum."""
         _dense(q_lat, "q_lat", torch.float32), _dense(latent_pages, "latent_pages"), _dense(out, "out", latent_pages.dtype)
         heads, seg, rank = q_lat.shape
         rot = rot_pages.shape[3] if rot_pages is not None else 0
@@ -1405,6 +1417,26 @@ class CudaKernels:
             raise KernelError("latent_attention: q_rot is [n, heads, rot] and rot_pages lies beside latent_pages")
         if sink is not None and _dense(sink, "sink").numel() != heads:
             raise KernelError("latent_attention: sink has one number per head")
+        if (not exact and max_q_len is not None and max_seq_len is not None and latent_pages.dtype == torch.bfloat16 and rank % 8 == 0
+                and rank <= 256 and rot % 8 == 0):
+            lib = self._lat_lib()
+            requests = cu_q.numel() - 1
+            ctas = requests * -(-int(max_q_len) * heads // 64)
+            reach = min(int(max_seq_len), int(window) + int(max_q_len)) if window else int(max_seq_len)
+            splits = max(1, min((2 * self.sm_count) // ctas, -(-reach // self.split_min_keys), 32))
+            need = lib.ifb_latent_attention_mma_scratch_floats(requests, int(max_q_len), heads, rank, splits)
+            if need * 4 > self.attention_scratch_cap:
+                splits, need = 1, 0
+            scratch = self.attention_scratch(need) if need else None
+            self.launches += 1 + (1 if splits > 1 else 0)
+            self.latent_mma_calls += 1
+            _check(lib.ifb_latent_attention_mma(q_lat.data_ptr(), _ptr(q_rot) if rot else None, seg, latent_pages.data_ptr(),
+                                                _ptr(rot_pages) if rot else None, block_tables.data_ptr(), block_tables.stride(0),
+                                                latent_pages.shape[2], cu_q.data_ptr(), seq_lens.data_ptr(), _ptr(sink),
+                                                _code(sink) if sink is not None else 0, out.data_ptr(), _ptr(scratch), requests,
+                                                int(max_q_len), heads, rank, rot, float(scale), int(window or 0), splits,
+                                                self._stream()), "latent_attention")
+            return
         self.launches += 1
         _check(self._lat_lib().ifb_latent_attention(q_lat.data_ptr(), _ptr(q_rot) if rot else None, seg, latent_pages.data_ptr(),
                                                     _ptr(rot_pages) if rot else None, _code(latent_pages), block_tables.data_ptr(),

@@ -42,6 +42,8 @@ class LatentAttention:
         self.w_o = weights[s.o_proj]
         self.sink = weights[s.sink] if s.sink is not None else None
         self.position = build_part(s.position, weights, runtime) if s.position is not None else None
+        import os
+        self.exact_weights = os.environ.get("INFURNACE_EXACT_ATTENTION", "0") not in ("", "0")
 
     def _segment(self, n):
         """Rows of a head's segment in the grouped products, and the tile of the tcgen05 route (0: the other route)."""
@@ -78,7 +80,8 @@ class LatentAttention:
             k.moe_linear(q_plain.view(H * seg, D), self.w_absorb, offsets, None, 1, q_lat)
         o_lat = ctx.buffer("la_o_lat", (H * seg, R), act, rows=H * cap)
         k.latent_attention(q_lat.view(H, seg, R), q_rot, lat_pages, rot_pages, kv.block_tables, ctx.cu_q, ctx.seq_lens, ctx.req_index,
-                           self.sink, o_lat.view(H, seg, R), s.scale, s.window or 0, n)
+                           self.sink, o_lat.view(H, seg, R), s.scale, s.window or 0, n, max_q_len=ctx.max_q_len,
+                           max_seq_len=ctx.max_seq_len, exact=self.exact_weights)
         y = ctx.buffer("la_y", (H * seg, V), torch.float32, rows=H * cap)
         if tile:
             k.moe_linear_grouped(o_lat, self.w_values, tiles, y)

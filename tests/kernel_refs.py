@@ -634,7 +634,7 @@ class ReferenceKernels:
             rot_pages.view(-1, rot)[slots[live]] = kr[live].to(rot_pages.dtype)
 
     def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
-                         window, tokens):
+                         window, tokens, max_q_len=None, max_seq_len=None, exact=False):
         """Every head of a token attends over its request's cached latents (and the shared rotated key part)."""
         heads, seg, rank = q_lat.shape
         ps = latent_pages.shape[2]

@@ -218,6 +218,17 @@ def _latent_case(K, H, D, V, R, rot, dims, ps, dtype, lens_new, lens_old, window
         K.latent_attention(q_lat.cuda(), qr_g, lat_g, rk_g, tables.cuda(), cu.cuda(), seq.cuda(), req.cuda(),
                            None if sinks is None else sinks.cuda(), got, scale, window, n)
         close(got[:, :n], want[:, :n], 2e-5 if dtype == torch.float32 else 0.05, "attention over latents")
+        if dtype == torch.bfloat16:
+            # with the step's extents: the tensor-core kernel where the sizes allow it, alone and with the context divided
+            for min_keys in (256, 64):
+                before, K.split_min_keys, keep = K.latent_mma_calls, min_keys, K.split_min_keys
+                got = torch.full((H, seg, R), float("nan"), device="cuda", dtype=dtype)
+                K.latent_attention(q_lat.cuda(), qr_g, lat_g, rk_g, tables.cuda(), cu.cuda(), seq.cuda(), req.cuda(),
+                                   None if sinks is None else sinks.cuda(), got, scale, window, n, max_q_len=max(lens_new),
+                                   max_seq_len=int(seq.max()))
+                K.split_min_keys = keep
+                assert (K.latent_mma_calls > before) == (R % 8 == 0 and R <= 256 and rot % 8 == 0)
+                close(got[:, :n], want[:, :n], 0.05 if plant is None else 0.12, "attention over latents on tensor cores")
         w_val = torch.randn(H, V, R, generator=g)
         y = torch.einsum("hsr,hvr->hsv", want.float(), w_val)
         gate = proj[:, down_col + R + rot:]
