@@ -46,7 +46,7 @@ constexpr float LM_LOG2E = 1.4426950408889634f;
 __host__ __device__ inline size_t lm_part_floats(int rank_pad) { return (size_t)LM_ROWS * (rank_pad + 2); }
 
 template <int RANK>          // columns of the latent in shared memory (the latent's width rounded up; the rest zeros)
-__global__ void __launch_bounds__(LM_THREADS)
+__global__ void __launch_bounds__(LM_THREADS, RANK <= 64 ? 4 : RANK <= 128 ? 3 : 2)
 latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, int seg, const bf16* __restrict__ lat_pages,
                             const bf16* __restrict__ rot_pages, const int* __restrict__ block_tables, int table_stride, int page_size,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_lens, const void* __restrict__ sink, int stype,
@@ -80,37 +80,34 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     ke = min(p_hi, kb + per - 1);
   }
   float* my_part = part ? part + ((size_t)(r * gridDim.x + blockIdx.x) * splits + split) * lm_part_floats(RANK) : nullptr;
-  // ---- the rows' queries: [latent-space part | rotated part], bfloat16
-  for (int i = tid; i < LM_ROWS * (KD / 2); i += LM_THREADS) {
-    const int row = i / (KD / 2), c = (i - row * (KD / 2)) * 2, rho = row0 + row;
-    float a = 0.f, b = 0.f;
-    if (rho < nrows) {
-      const int t = q0 + rho / heads, h = rho % heads;
-      if (c < rank) {
-        const float2 v = *reinterpret_cast<const float2*>(q_lat + ((size_t)h * seg + t) * rank + c);
-        a = v.x; b = v.y;
-      } else if (c >= RANK && c - RANK < rot) {
-        const float2 v = *reinterpret_cast<const float2*>(q_rot + ((size_t)t * heads + h) * rot + (c - RANK));
-        a = v.x; b = v.y;
-      }
+  // ---- the rows' queries: [latent-space part | rotated part], bfloat16; two threads per row, a pair of columns at a time
+  {
+    const int row = tid >> 1, rho = row0 + row;
+    const bool live = rho < nrows;
+    const int t = live ? q0 + rho / heads : 0, h = live ? rho % heads : 0;
+    const float* ql = q_lat + ((size_t)h * seg + t) * rank;
+    const float* qr = q_rot + ((size_t)t * heads + h) * rot;
+    bf16* dst = Qs + (size_t)row * LD;
+    for (int c = (tid & 1) * 2; c < KD; c += 4) {
+      float a = 0.f, b = 0.f;
+      if (live && c < rank) { const float2 v = *reinterpret_cast<const float2*>(ql + c); a = v.x; b = v.y; }
+      else if (live && c >= RANK && c - RANK < rot) { const float2 v = *reinterpret_cast<const float2*>(qr + (c - RANK)); a = v.x; b = v.y; }
+      *reinterpret_cast<uint32_t*>(dst + c) = lm_pack(a, b);
     }
-    *reinterpret_cast<uint32_t*>(Qs + (size_t)row * LD + c) = lm_pack(a, b);
   }
   const int* table = block_tables + (size_t)r * table_stride;
-  const int chunks = KD / 8;                       // 16-byte pieces of a row
+  // two threads per key: one look at the block table per thread and tile, then 16-byte pieces of the row alternately
   auto load_tile = [&](int tile0, int stage) {
-    bf16* dst = Ks + (size_t)stage * LM_KEYS * LD;
-    for (int i = tid; i < LM_KEYS * chunks; i += LM_THREADS) {
-      const int key = i / chunks, c = (i - key * chunks) * 8, j = tile0 + key;
-      const bool live = j >= kb && j <= ke;
-      const bf16* src = lat_pages;
-      bool valid = false;
-      if (live) {
-        const size_t slot = (size_t)table[j / page_size] * page_size + j % page_size;
-        if (c < rank) { src = lat_pages + slot * rank + c; valid = true; }
-        else if (c >= RANK && c - RANK < rot) { src = rot_pages + slot * rot + (c - RANK); valid = true; }
-      }
-      lm_cp16(dst + (size_t)key * LD + c, src, valid);
+    const int key = tid >> 1, j = tile0 + key;
+    bf16* dst = Ks + ((size_t)stage * LM_KEYS + key) * LD;
+    const bool live = j >= kb && j <= ke;
+    size_t slot = 0;
+    if (live) slot = (size_t)table[j / page_size] * page_size + j % page_size;
+    const bf16* lat = lat_pages + slot * rank;
+    const bf16* rk = rot_pages + slot * rot;
+    for (int c = (tid & 1) * 8; c < KD; c += 16) {
+      const bool in_lat = c < rank, in_rot = c >= RANK && c - RANK < rot;
+      lm_cp16(dst + c, in_lat ? lat + c : in_rot ? rk + (c - RANK) : lat_pages, live && (in_lat || in_rot));
     }
   };
   float o[RANK / 8][4];
@@ -235,36 +232,41 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   }
 }
 
-// The split form's second step: per row the maximum over the splits (and the sink), the denominators and sums brought to
-// it, and the quotient.  A warp per row.
+// The split form's second step, a block per row: the maximum over the splits (and the sink), every split's weight
+// 2^(m_z - m), the denominator, and the weighted sums' quotient.  The first warp forms the weights (at most 32 splits).
 template <int RANK>
 __global__ void __launch_bounds__(LM_THREADS)
 latent_attention_merge_kernel(const float* __restrict__ part, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                               const void* __restrict__ sink, int stype, bf16* __restrict__ out, int seg, int heads, int rank,
-                              int splits) {
+                              int splits, int tiles) {
+  __shared__ float wz[32];
+  __shared__ float inv_l;
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = cu_q[r], nrows = (cu_q[r + 1] - q0) * heads, row0 = blockIdx.x * LM_ROWS;
-  if (row0 >= nrows || seq_lens[r] <= 0) return;
+  const int r = blockIdx.y, rho = blockIdx.x, lane = threadIdx.x & 31;
+  const int q0 = cu_q[r], nrows = (cu_q[r + 1] - q0) * heads;
+  if (rho >= nrows || seq_lens[r] <= 0) return;
+  const int tile = rho / LM_ROWS, row = rho - tile * LM_ROWS, h = rho % heads;
   const size_t PF = lm_part_floats(RANK);
-  const float* base = part + (size_t)(r * gridDim.x + blockIdx.x) * splits * PF;
-  for (int row = warp; row < min(LM_ROWS, nrows - row0); row += LM_THREADS / 32) {
-    const int rho = row0 + row, h = rho % heads;
+  const float* base = part + (size_t)(r * tiles + tile) * splits * PF;
+  if (threadIdx.x < 32) {
     const float s2 = sink != nullptr ? load_as_f32(sink, stype, h) * LM_LOG2E : -INFINITY;
-    float m = s2;
-    for (int z = 0; z < splits; ++z) m = fmaxf(m, base[z * PF + (size_t)LM_ROWS * RANK + row]);
-    float l = sink != nullptr ? exp2f(s2 - m) : 0.f;
-    for (int z = 0; z < splits; ++z)
-      l = fmaf(base[z * PF + (size_t)LM_ROWS * RANK + LM_ROWS + row], exp2f(base[z * PF + (size_t)LM_ROWS * RANK + row] - m), l);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    bf16* dst = out + ((size_t)h * seg + q0 + rho / heads) * rank;
-    for (int c = lane; c < rank; c += 32) {
-      float acc = 0.f;
-      for (int z = 0; z < splits; ++z)
-        acc = fmaf(base[z * PF + (size_t)row * RANK + c], exp2f(base[z * PF + (size_t)LM_ROWS * RANK + row] - m), acc);
-      dst[c] = __float2bfloat16(acc * inv);
-    }
+    const float mz = lane < splits ? base[lane * PF + (size_t)LM_ROWS * RANK + row] : -INFINITY;
+    const float lz = lane < splits ? base[lane * PF + (size_t)LM_ROWS * RANK + LM_ROWS + row] : 0.f;
+    const float m = fmaxf(warp_max(mz), s2);
+    const float w = mz == -INFINITY ? 0.f : exp2f(mz - m);
+    float l = warp_sum(lz * w);
+    if (sink != nullptr) l += exp2f(s2 - m);
+    wz[lane] = w;
+    if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
+  bf16* dst = out + ((size_t)h * seg + q0 + rho / heads) * rank;
+  for (int c = threadIdx.x; c < rank; c += LM_THREADS) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int z = 0; z < splits; ++z) acc = fmaf(base[z * PF + (size_t)row * RANK + c], wz[z], acc);
+    dst[c] = __float2bfloat16(acc * inv_l);
   }
 }
 
@@ -291,8 +293,8 @@ static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void
                       (const bf16*)rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, (bf16*)out, part, heads,
                       rank, rot, rot_pad, scale, window, splits);
   if (rc != IFB_OK || splits <= 1) return rc;
-  return ifb_launch(latent_attention_merge_kernel<RANK>, dim3(grid.x, grid.y), dim3(LM_THREADS), 0, stream, (const float*)part, cu_q,
-                    seq_lens, sink, stype, (bf16*)out, seg, heads, rank, splits);
+  return ifb_launch(latent_attention_merge_kernel<RANK>, dim3((unsigned)(max_q_len * heads), grid.y), dim3(LM_THREADS), 0, stream,
+                    (const float*)part, cu_q, seq_lens, sink, stype, (bf16*)out, seg, heads, rank, splits, (int)grid.x);
 }
 
 // bfloat16 pages and outputs; rank and rot multiples of 8, rank at most 256.
@@ -301,7 +303,7 @@ IFB_EXPORT int ifb_latent_attention_mma(const float* q_lat, const float* q_rot, 
                                         const void* sink, int stype, void* out, float* part, int requests, int max_q_len, int heads,
                                         int rank, int rot, float scale, int window, int splits, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return IFB_OK;
-  if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 ||
+  if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 || splits > 32 ||
       (splits > 1 && part == nullptr))
     return IFB_ERR_SIZE;
 #define LM_CASE(P)                                                                                                             \

@@ -1423,7 +1423,7 @@ class CudaKernels:
             requests = cu_q.numel() - 1
             ctas = requests * -(-int(max_q_len) * heads // 64)
             reach = min(int(max_seq_len), int(window) + int(max_q_len)) if window else int(max_seq_len)
-            splits = max(1, min((2 * self.sm_count) // ctas, -(-reach // self.split_min_keys), 32))
+            splits = max(1, min((2 * self.sm_count) // ctas, -(-reach // max(64, self.split_min_keys // 2)), 32))
             need = lib.ifb_latent_attention_mma_scratch_floats(requests, int(max_q_len), heads, rank, splits)
             if need * 4 > self.attention_scratch_cap:
                 splits, need = 1, 0
