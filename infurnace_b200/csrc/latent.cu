@@ -123,7 +123,7 @@ IFB_EXPORT int ifb_depth_average(float* x, const float* delta, float mult, float
 // state by the portion's last K inputs (older ones shifted down where the portion is shorter), so that each element of the
 // state is read and written by one thread only; the blocks of those other tokens do nothing.
 // ------------------------------------------------------------------------------------------
-constexpr int CC_MAX_TAPS = 16;
+constexpr int CC_MAX_TAPS = 64;
 template <typename T>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int wtype, float* __restrict__ state,
@@ -151,20 +151,16 @@ causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int
   float* st = state + (size_t)state_slots[r] * (K > 0 ? K : 1) * width;
   const int head = len < K ? len : K;                  // tokens of the portion that read the state
   for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    float seq[2 * CC_MAX_TAPS];                        // inputs -K .. head - 1 of the portion, at index + K
-    float w[CC_MAX_TAPS];
-    for (int k = 0; k < K; ++k) seq[k] = st[(size_t)k * width + e];
-    for (int k = 0; k < head; ++k) seq[K + k] = to_f32<T>(h[(size_t)(q0 + k) * width + e]);
-    for (int j = 0; j <= K; ++j) w[j] = load_as_f32(weight, wtype, (size_t)e * taps + j);
+    // input number x of the portion (x < 0: from the state, which holds inputs -K .. -1 at 0 .. K - 1)
+    auto input = [&](int x) { return x < 0 ? st[(size_t)(K + x) * width + e] : to_f32<T>(h[(size_t)(q0 + x) * width + e]); };
     for (int k = 0; k < head; ++k) {
-      float acc = seq[K + k];
-      for (int j = 0; j <= K; ++j) acc = fmaf(w[j], seq[k + j], acc);
+      float acc = input(k);
+      for (int j = 0; j <= K; ++j) acc = fmaf(load_as_f32(weight, wtype, (size_t)e * taps + j), input(k - K + j), acc);
       out[(size_t)(q0 + k) * width + e] = from_f32<T>(acc);
     }
-    for (int k = 0; k < K; ++k) {                      // the new state: inputs len - K + k
-      const int idx = len - K + k;
-      st[(size_t)k * width + e] = idx < head ? seq[K + idx] : to_f32<T>(h[(size_t)(q0 + idx) * width + e]);
-    }
+    // the new state: inputs len - K .. len - 1.  Place k takes input len - K + k, which is the old place len + k when that is
+    // still a state's input: a place above k, so ascending k reads nothing that was written.
+    for (int k = 0; k < K; ++k) st[(size_t)k * width + e] = input(len - K + k);
   }
 }
 
