@@ -60,7 +60,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   ifb_pdl_trigger();
   const int r = blockIdx.y, split = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q0 = cu_q[r], nq = cu_q[r + 1] - q0, L = seq_lens[r];
-  const int nrows = nq * heads, row0 = blockIdx.x * LM_ROWS;
+  // the last rows of a request see the most keys: they start first, so that the grid's tail is made of short CTAs
+  const int tile_x = gridDim.x - 1 - blockIdx.x;
+  const int nrows = nq * heads, row0 = tile_x * LM_ROWS;
   if (row0 >= nrows) return;
   if (L <= 0) {                                    // a padding request of a recorded step: zeros
     if (split == 0)
@@ -79,7 +81,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     kb = k_lo + split * per;
     ke = min(p_hi, kb + per - 1);
   }
-  float* my_part = part ? part + ((size_t)(r * gridDim.x + blockIdx.x) * splits + split) * lm_part_floats(RANK) : nullptr;
+  float* my_part = part ? part + ((size_t)(r * gridDim.x + tile_x) * splits + split) * lm_part_floats(RANK) : nullptr;
   // ---- the rows' queries: [latent-space part | rotated part], bfloat16; two threads per row, a pair of columns at a time
   {
     const int row = tid >> 1, rho = row0 + row;
@@ -96,13 +98,18 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     }
   }
   const int* table = block_tables + (size_t)r * table_stride;
-  // two threads per key: one look at the block table per thread and tile, then 16-byte pieces of the row alternately
-  auto load_tile = [&](int tile0, int stage) {
-    const int key = tid >> 1, j = tile0 + key;
-    bf16* dst = Ks + ((size_t)stage * LM_KEYS + key) * LD;
+  // two threads per key: one look at the block table per thread and tile (made one tile ahead, so that no copy waits for
+  // it), then 16-byte pieces of the row alternately
+  const int my_key = tid >> 1;
+  auto page_of = [&](int tile0) {
+    const int j = tile0 + my_key;
+    return j >= kb && j <= ke ? table[j / page_size] : 0;
+  };
+  auto load_tile = [&](int tile0, int stage, int page) {
+    const int j = tile0 + my_key;
+    bf16* dst = Ks + ((size_t)stage * LM_KEYS + my_key) * LD;
     const bool live = j >= kb && j <= ke;
-    size_t slot = 0;
-    if (live) slot = (size_t)table[j / page_size] * page_size + j % page_size;
+    const size_t slot = live ? (size_t)page * page_size + j % page_size : 0;
     const bf16* lat = lat_pages + slot * rank;
     const bf16* rk = rot_pages + slot * rot;
     for (int c = (tid & 1) * 8; c < KD; c += 16) {
@@ -126,11 +133,13 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const bool warp_live = row0 + warp * 16 < nrows;
   const float sc = scale * LM_LOG2E;
   const int ntiles = ke >= kb ? (ke - kb) / LM_KEYS + 1 : 0;
-  if (ntiles > 0) load_tile(kb, 0);
+  if (ntiles > 0) load_tile(kb, 0, page_of(kb));
   lm_commit();
+  int page_next = ntiles > 1 ? page_of(kb + LM_KEYS) : 0;
   for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) load_tile(kb + (it + 1) * LM_KEYS, (it + 1) & 1);
+    if (it + 1 < ntiles) load_tile(kb + (it + 1) * LM_KEYS, (it + 1) & 1, page_next);
     lm_commit();
+    if (it + 2 < ntiles) page_next = page_of(kb + (it + 2) * LM_KEYS);
     lm_wait<1>();
     __syncthreads();
     const int tile0 = kb + it * LM_KEYS;
