@@ -124,14 +124,14 @@ IFB_EXPORT int ifb_depth_average(float* x, const float* delta, float mult, float
 // state is read and written by one thread only; the blocks of those other tokens do nothing.
 // ------------------------------------------------------------------------------------------
 constexpr int CC_MAX_TAPS = 64;
-template <typename T>
-__global__ void __launch_bounds__(256)
-causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int wtype, float* __restrict__ state,
-                   const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
-                   const int* __restrict__ req_index, T* __restrict__ out, int width, int taps) {
-  ifb_pdl_wait();
-  ifb_pdl_trigger();
-  const int t = blockIdx.x, K = taps - 1;
+// VT > 0 (bfloat16 rows and weights, a multiple of 8 channels, 16-byte aligned, VT = taps): the tokens that read no state
+// take eight channels per thread: the channels' VT x 8 weights and each tap's eight inputs are 16-byte loads.
+template <typename T, int VT>
+__device__ __forceinline__ void causal_conv_token(int t, const T* __restrict__ h, const void* __restrict__ weight, int wtype,
+                                                  float* __restrict__ state, const int* __restrict__ state_slots,
+                                                  const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                                                  const int* __restrict__ req_index, T* __restrict__ out, int width, int taps) {
+  const int K = taps - 1;
   const int r = req_index[t];
   const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
   if (seq_lens[r] <= 0) {                              // a padding row of a recorded step: it stores and sees nothing
@@ -140,11 +140,33 @@ causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int
   }
   if (i > 0 && i < K) return;                          // the first token's block computes these
   if (i >= K) {
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-      float acc = to_f32<T>(h[(size_t)t * width + e]);
-      for (int j = 0; j <= K; ++j)
-        acc = fmaf(load_as_f32(weight, wtype, (size_t)e * taps + j), to_f32<T>(h[(size_t)(t - K + j) * width + e]), acc);
-      out[(size_t)t * width + e] = from_f32<T>(acc);
+    if constexpr (VT > 0) {
+      const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(weight);
+      for (int e = threadIdx.x * 8; e < width; e += blockDim.x * 8) {
+        __align__(16) __nv_bfloat16 w[VT * 8];          // w[c * VT + j]
+        __align__(16) __nv_bfloat16 x[VT * 8];          // x[j * 8 + c]
+#pragma unroll
+        for (int v = 0; v < VT; ++v) {
+          *reinterpret_cast<uint4*>(w + 8 * v) = *reinterpret_cast<const uint4*>(wb + (size_t)e * VT + 8 * v);
+          *reinterpret_cast<uint4*>(x + 8 * v) = *reinterpret_cast<const uint4*>(h + (size_t)(t - (VT - 1) + v) * width + e);
+        }
+        __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float acc = __bfloat162float(x[(VT - 1) * 8 + c]);
+#pragma unroll
+          for (int j = 0; j < VT; ++j) acc = fmaf(__bfloat162float(w[c * VT + j]), __bfloat162float(x[j * 8 + c]), acc);
+          o[c] = __float2bfloat16(acc);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * width + e) = *reinterpret_cast<const uint4*>(o);
+      }
+    } else {
+      for (int e = threadIdx.x; e < width; e += blockDim.x) {
+        float acc = to_f32<T>(h[(size_t)t * width + e]);
+        for (int j = 0; j <= K; ++j)
+          acc = fmaf(load_as_f32(weight, wtype, (size_t)e * taps + j), to_f32<T>(h[(size_t)(t - K + j) * width + e]), acc);
+        out[(size_t)t * width + e] = from_f32<T>(acc);
+      }
     }
     return;
   }
@@ -164,17 +186,40 @@ causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int
   }
 }
 
+template <typename T, int VT>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const T* __restrict__ h, const void* __restrict__ weight, int wtype, float* __restrict__ state,
+                   const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                   const int* __restrict__ req_index, T* __restrict__ out, int width, int taps) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  causal_conv_token<T, VT>(blockIdx.x, h, weight, wtype, state, state_slots, cu_q, seq_lens, req_index, out, width, taps);
+}
+
 IFB_EXPORT int ifb_causal_conv(const void* h, int dtype, const void* weight, int wtype, float* state, const int* state_slots,
                                const int* cu_q, const int* seq_lens, const int* req_index, void* out, int tokens, int width,
                                int taps, cudaStream_t stream) {
   if (tokens <= 0) return IFB_OK;
   if (width < 1 || taps < 1 || taps > CC_MAX_TAPS) return IFB_ERR_SIZE;
   const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
-  if (dtype == IFB_BF16)
-    return ifb_launch(causal_conv_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)h, weight,
+  const dim3 grid((unsigned)tokens);
+  if (dtype == IFB_BF16) {
+    // rows that read no state go eight channels at a time where the taps are few and everything is aligned
+    if (wtype == IFB_BF16 && taps >= 2 && taps <= 8 && width % 8 == 0 && width >= 256 &&
+        (((uintptr_t)h | (uintptr_t)out | (uintptr_t)weight) & 15) == 0) {
+#define CC_VEC(V)                                                                                                              \
+  case V:                                                                                                                      \
+    return ifb_launch(causal_conv_kernel<__nv_bfloat16, V>, grid, dim3(width >= 2048 ? 256 : 128), 0, stream,                  \
+                      (const __nv_bfloat16*)h, weight, wtype, state, state_slots, cu_q, seq_lens, req_index, (__nv_bfloat16*)out, \
+                      width, taps)
+      switch (taps) { CC_VEC(2); CC_VEC(3); CC_VEC(4); CC_VEC(5); CC_VEC(6); CC_VEC(7); CC_VEC(8); }
+#undef CC_VEC
+    }
+    return ifb_launch(causal_conv_kernel<__nv_bfloat16, 0>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)h, weight,
                       wtype, state, state_slots, cu_q, seq_lens, req_index, (__nv_bfloat16*)out, width, taps);
+  }
   if (dtype != IFB_F32) return IFB_ERR_DTYPE;
-  return ifb_launch(causal_conv_kernel<float>, dim3(tokens), dim3(threads), 0, stream, (const float*)h, weight, wtype, state,
+  return ifb_launch(causal_conv_kernel<float, 0>, grid, dim3(threads), 0, stream, (const float*)h, weight, wtype, state,
                     state_slots, cu_q, seq_lens, req_index, (float*)out, width, taps);
 }
 

@@ -119,10 +119,10 @@ def test_average_over_depth(K, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,width", [(4, 320), (1, 40), (2, 33), (3, 1000), (6, 64), (16, 8)])
+@pytest.mark.parametrize("taps,width", [(4, 320), (1, 40), (2, 33), (3, 1000), (6, 64), (16, 8), (5, 2048), (40, 264)])
 def test_input_convolution_over_steps_and_slots(K, dtype, taps, width):
     """Requests advance by portions of every length around the convolution's reach; what a token sees never depends on the
-    cutting: the last step's outputs equal the convolution over the whole sequences."""
+    cutting: every step's outputs equal the convolution over the whole sequences."""
     g = gen(taps * width)
     w = (0.5 * torch.randn(width, taps, generator=g)).to(torch.bfloat16)
     state_r = torch.zeros(9, max(taps - 1, 1), width)
@@ -130,7 +130,7 @@ def test_input_convolution_over_steps_and_slots(K, dtype, taps, width):
     whole = [torch.randn(0, width).to(dtype) for _ in range(4)]
     outs = [[] for _ in range(4)]
     old = [0, 0, 0, 0]
-    for lens in ([1, taps + 3, 2, 40], [1, 1, 1, taps], [2, 1, taps - 1 or 1, 1], [taps, 2, 1, 70], [1, 1, 2, 1]):
+    for lens in ([1, taps + 3, 2, 40], [1, 1, 1, taps], [2, 1, taps - 1 or 1, 1], [taps, 2, 1, 70], [300, 701, 1, 200], [1, 1, 2, 1]):
         cu, seq, slots, req = requests(lens, old, pad=2)
         n = int(cu[-1])
         h = torch.randn(n, width, generator=g).to(dtype)
