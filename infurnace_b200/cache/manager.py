@@ -55,7 +55,7 @@ class KVGroup:
     def uniform(self) -> bool:
         """All streams have one shape, so an entry is a single tensor with a stream axis."""
         st = self.need.streams
-        return all((x.heads, x.width) == (st[0].heads, st[0].width) for x in st)
+        return not getattr(self.need, "separate", False) and all((x.heads, x.width) == (st[0].heads, st[0].width) for x in st)
 
     def first_needed_page(self, next_position: int) -> int:
         """Index of the first logical page that the query at ``next_position`` can read."""

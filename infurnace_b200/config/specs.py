@@ -80,13 +80,15 @@ class PagedCacheNeed:
     small rotated key, say, instead of full keys and values), with the same window rule as
     :class:`KVCacheNeed`.  A cache entry then has one tensor per stream,
     ``[pages, heads, page_size, width]``; streams of equal shape share one tensor
-    ``[pages, streams, heads, page_size, width]`` (which is the layout of keys and values)."""
+    ``[pages, streams, heads, page_size, width]`` (which is the layout of keys and values) unless ``separate`` asks
+    for a dense tensor per stream whatever the shapes (kernels that address a stream as ``[pages * page_size, width]``)."""
     streams: Tuple[PagedStream, ...]
     window: Optional[int] = None
+    separate: bool = False
 
     @property
     def group_key(self):
-        return ("kv", self.streams, self.window)
+        return ("kv", self.streams, self.window, self.separate)
 
 
 @dataclass(frozen=True)
@@ -744,7 +746,7 @@ class LatentAttentionSpec:
         streams = (PagedStream("latent", 1, self.kv_rank),)
         if self.rot_dim:
             streams += (PagedStream("rotated_key", 1, self.rot_dim),)
-        return PagedCacheNeed(streams, self.window)
+        return PagedCacheNeed(streams, self.window, separate=True)      # also where kv_rank == rot_dim
 
 
 @dataclass(frozen=True)

@@ -91,6 +91,19 @@ def test_cache_entries_hold_the_latent_and_the_convolutions_inputs():
     assert all(float(t[slot].abs().max()) == 0.0 for g in cache.state_groups for t in g.tensors.values())
 
 
+def test_a_latent_and_a_rotated_key_of_one_width_keep_a_dense_tensor_each():
+    """Streams of equal shape would share one tensor with a stream axis; the latent kernels address a stream as
+    [pages * page_size, width], so this need asks for a tensor per stream."""
+    conf = TF._config(30, 16, 1e-5, 1, 1.0, 2, [TF._rot(2, 8, 12, 8, 12, 0.3, 100.0, None)])
+    plan = plan_for(config_from_dict(conf))
+    cache = CacheManager(plan, page_size=4, num_pages=5, max_requests=2, dtype=torch.float32, device="cpu")
+    (g,) = cache.kv_groups
+    (streams,) = g.streams.values()
+    assert set(streams) == {"latent", "rotated_key"}
+    assert all(t.is_contiguous() and tuple(t.shape) == (5, 1, 4, 12) for t in streams.values())
+    assert streams["latent"].data_ptr() != streams["rotated_key"].data_ptr()
+
+
 def test_configuration_faults_are_named():
     base = TF.TINY["F1"]["config"]
 

@@ -379,6 +379,11 @@ OTHER_SIZES = {
         TF._win(8, 64, 64, 128, 0.1, 64, TF._moe(8, 2, 32, groups=(4, 1), scale=1.5)),
         TF._rot(4, 64, 64, 64, 256, 0.1, 20.0, None),
         TF._win(2, 128, 128, 64, 0.08, 17, TF._moe(4, 1, 128, shared=128), plain=True)])},
+    # a latent and a rotated key part of one width (their page streams have the same shape), with one head and with several
+    "equal": TF._config(61, 64, 1e-5, 2, 0.5, 3, [
+        TF._rot(3, 16, 32, 16, 32, 0.2, 100.0, TF._moe(4, 2, 32, groups=(2, 1), shared=16)),
+        TF._win(2, 16, 16, 32, 0.25, 21, None),
+        TF._rot(1, 8, 16, 24, 16, 0.3, 10000.0, TF._moe(2, 1, 16))]),
     # a single layer: the average over depth of the embedding's output and one result
     "one": TF._config(40, 32, 1e-5, 2, 1.0, 3, [TF._win(1, 32, 16, 16, 0.2, 10, TF._moe(4, 2, 16, groups=(2, 1)))]),
 }
