@@ -40,12 +40,21 @@ __device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// 2^x of a weight that is rounded to bfloat16 next: the approximation's error is far below that rounding
+__device__ __forceinline__ float lm_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 constexpr float LM_LOG2E = 1.4426950408889634f;
 
 // Scratch of the split form, per (request, row tile, split): 64 rows of RANK sums, then 64 maxima, then 64 denominators.
 __host__ __device__ inline size_t lm_part_floats(int rank_pad) { return (size_t)LM_ROWS * (rank_pad + 2); }
 
-template <int RANK>          // columns of the latent in shared memory (the latent's width rounded up; the rest zeros)
+// RANK: columns of the latent in shared memory (the latent's width rounded up; the rest zeros).  ROTP: the rotated part's
+// columns there, known when the kernel is compiled (row length, offsets of every ldmatrix and the trip counts are then
+// constants), or -1: the argument rot_pad says.
+template <int RANK, int ROTP>
 __global__ void __launch_bounds__(LM_THREADS, RANK <= 64 ? 4 : RANK <= 128 ? 3 : 2)
 latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, int seg, const bf16* __restrict__ lat_pages,
                             const bf16* __restrict__ rot_pages, const int* __restrict__ block_tables, int table_stride, int page_size,
@@ -53,6 +62,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
                             bf16* __restrict__ out, float* __restrict__ part, int heads, int rank, int rot, int rot_pad,
                             float scale, int window, int splits) {
   extern __shared__ __align__(16) unsigned char lm_raw[];
+  if (ROTP >= 0) rot_pad = ROTP;
   const int KD = RANK + rot_pad, LD = KD + 8;      // columns of a row, and its length in shared memory
   bf16* Qs = reinterpret_cast<bf16*>(lm_raw);
   bf16* Ks = Qs + (size_t)LM_ROWS * LD;            // two stages of LM_KEYS rows
@@ -151,6 +161,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       float s[LM_KEYS / 8][4];
 #pragma unroll
       for (int n = 0; n < LM_KEYS / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll(ROTP >= 0 ? (RANK + (ROTP >= 0 ? ROTP : 0)) / 16 : 1)
       for (int kk = 0; kk < KD / 16; ++kk) {
         uint32_t a[4];
         lm_ldm(a, Qs + (size_t)(warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
@@ -185,8 +196,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       float sumA = 0.f, sumB = 0.f;
 #pragma unroll
       for (int n = 0; n < LM_KEYS / 8; ++n) {
-        s[n][0] = exp2f(s[n][0] - baseA); s[n][1] = exp2f(s[n][1] - baseA);
-        s[n][2] = exp2f(s[n][2] - baseB); s[n][3] = exp2f(s[n][3] - baseB);
+        s[n][0] = lm_ex2(s[n][0] - baseA); s[n][1] = lm_ex2(s[n][1] - baseA);
+        s[n][2] = lm_ex2(s[n][2] - baseB); s[n][3] = lm_ex2(s[n][3] - baseB);
         sumA += s[n][0] + s[n][1];
         sumB += s[n][2] + s[n][3];
       }
@@ -288,7 +299,7 @@ IFB_EXPORT long long ifb_latent_attention_mma_scratch_floats(int requests, int m
   return (long long)requests * tiles * splits * (long long)lm_part_floats(lm_rank_pad(rank));
 }
 
-template <int RANK>
+template <int RANK, int ROTP>
 static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void* lat_pages, const void* rot_pages, const int* block_tables,
                      int table_stride, int page_size, const int* cu_q, const int* seq_lens, const void* sink, int stype, void* out,
                      float* part, int requests, int max_q_len, int heads, int rank, int rot, float scale, int window, int splits,
@@ -296,9 +307,9 @@ static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void
   const int rot_pad = (rot + 15) / 16 * 16, LD = RANK + rot_pad + 8;
   const size_t smem = (size_t)(LM_ROWS + 2 * LM_KEYS) * LD * sizeof(bf16);
   if (smem > 220 * 1024) return IFB_ERR_SIZE;
-  IFB_ALLOW_SMEM(latent_attention_mma_kernel<RANK>, smem);
+  IFB_ALLOW_SMEM((latent_attention_mma_kernel<RANK, ROTP>), smem);
   const dim3 grid((unsigned)(((long long)max_q_len * heads + LM_ROWS - 1) / LM_ROWS), (unsigned)requests, (unsigned)splits);
-  int rc = ifb_launch(latent_attention_mma_kernel<RANK>, grid, dim3(LM_THREADS), smem, stream, q_lat, q_rot, seg, (const bf16*)lat_pages,
+  int rc = ifb_launch(latent_attention_mma_kernel<RANK, ROTP>, grid, dim3(LM_THREADS), smem, stream, q_lat, q_rot, seg, (const bf16*)lat_pages,
                       (const bf16*)rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, (bf16*)out, part, heads,
                       rank, rot, rot_pad, scale, window, splits);
   if (rc != IFB_OK || splits <= 1) return rc;
@@ -315,14 +326,24 @@ IFB_EXPORT int ifb_latent_attention_mma(const float* q_lat, const float* q_rot, 
   if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 || splits > 32 ||
       (splits > 1 && part == nullptr))
     return IFB_ERR_SIZE;
-#define LM_CASE(P)                                                                                                             \
-  return lm_launch<P>(q_lat, q_rot, seg, lat_pages, rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, \
-                      out, part, requests, max_q_len, heads, rank, rot, scale, window, splits, stream)
+#define LM_ARGS                                                                                                                \
+  q_lat, q_rot, seg, lat_pages, rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, out, part, requests, \
+      max_q_len, heads, rank, rot, scale, window, splits, stream
+  // the usual widths of a rotated part have kernels of their own; any other width runs the one that reads it at run time
+#define LM_CASE(P)                                            \
+  switch ((rot + 15) / 16 * 16) {                             \
+    case 0: return lm_launch<P, 0>(LM_ARGS);                  \
+    case 16: return lm_launch<P, 16>(LM_ARGS);                \
+    case 32: return lm_launch<P, 32>(LM_ARGS);                \
+    case 64: return lm_launch<P, 64>(LM_ARGS);                \
+    default: return lm_launch<P, -1>(LM_ARGS);                \
+  }
   switch (lm_rank_pad(rank)) {
-    case 32: LM_CASE(32);
+    case 32: return lm_launch<32, -1>(LM_ARGS);
     case 64: LM_CASE(64);
     case 128: LM_CASE(128);
     default: LM_CASE(256);
   }
 #undef LM_CASE
+#undef LM_ARGS
 }
