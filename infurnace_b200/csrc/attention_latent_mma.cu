@@ -174,17 +174,30 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
         }
       }
       float mxA = -INFINITY, mxB = -INFINITY;
+      // a tile that every row of the warp sees whole (no row ends inside it, no window starts inside it, none of its keys
+      // belongs to another split or lies beyond the rows) needs no mask
+      const bool whole = row0 + warp * 16 + 15 < nrows && tile0 + LM_KEYS - 1 <= min(w_lo_row, ke) && tile0 >= kb &&
+                         (window == 0 || tile0 >= w_hi - window + 1);
+      if (whole) {
 #pragma unroll
-      for (int n = 0; n < LM_KEYS / 8; ++n) {
+        for (int n = 0; n < LM_KEYS / 8; ++n) {
+          s[n][0] *= sc; s[n][1] *= sc; s[n][2] *= sc; s[n][3] *= sc;
+          mxA = fmaxf(mxA, fmaxf(s[n][0], s[n][1]));
+          mxB = fmaxf(mxB, fmaxf(s[n][2], s[n][3]));
+        }
+      } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int key = tile0 + n * 8 + (lane & 3) * 2 + (c & 1);
-          const bool second = c >= 2;
-          const int p = second ? pB : pA, lo = second ? loB : loA;
-          const bool see = key <= p && key >= lo && key >= kb && key <= ke;
-          const float v = see ? s[n][c] * sc : -INFINITY;
-          s[n][c] = v;
-          if (second) mxB = fmaxf(mxB, v); else mxA = fmaxf(mxA, v);
+        for (int n = 0; n < LM_KEYS / 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int key = tile0 + n * 8 + (lane & 3) * 2 + (c & 1);
+            const bool second = c >= 2;
+            const int p = second ? pB : pA, lo = second ? loB : loA;
+            const bool see = key <= p && key >= lo && key >= kb && key <= ke;
+            const float v = see ? s[n][c] * sc : -INFINITY;
+            s[n][c] = v;
+            if (second) mxB = fmaxf(mxB, v); else mxA = fmaxf(mxA, v);
+          }
         }
       }
       mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
@@ -203,8 +216,10 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       }
       lA = fmaf(lA, cA, sumA);
       lB = fmaf(lB, cB, sumB);
+      if (__any_sync(0xffffffffu, cA != 1.f || cB != 1.f)) {      // else no row's maximum moved: the sums stay as they are
 #pragma unroll
-      for (int n = 0; n < RANK / 8; ++n) { o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB; }
+        for (int n = 0; n < RANK / 8; ++n) { o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB; }
+      }
 #pragma unroll
       for (int ks = 0; ks < LM_KEYS / 16; ++ks) {
         uint32_t a[4] = {lm_pack(s[2 * ks][0], s[2 * ks][1]), lm_pack(s[2 * ks][2], s[2 * ks][3]),
