@@ -172,6 +172,49 @@ __device__ __forceinline__ void causal_conv_token(int t, const T* __restrict__ h
   }
   float* st = state + (size_t)state_slots[r] * (K > 0 ? K : 1) * width;
   const int head = len < K ? len : K;                  // tokens of the portion that read the state
+  if constexpr (VT > 0) {
+    // eight channels per thread here too (the state's rows are 16-byte aligned with the rest): the loads of a token's
+    // inputs are independent of one another, and this one block is what a step of single tokens waits for
+    const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(weight);
+    for (int e = threadIdx.x * 8; e < width; e += blockDim.x * 8) {
+      __align__(16) __nv_bfloat16 w[VT * 8];            // w[c * VT + j]
+#pragma unroll
+      for (int v = 0; v < VT; ++v) *reinterpret_cast<uint4*>(w + 8 * v) = *reinterpret_cast<const uint4*>(wb + (size_t)e * VT + 8 * v);
+      auto input8 = [&](int x, float (&v)[8]) {         // input number x of the portion, x < 0: from the state
+        if (x < 0) {
+          const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(K + x) * width + e);
+          const float4 b = *reinterpret_cast<const float4*>(st + (size_t)(K + x) * width + e + 4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+          __align__(16) __nv_bfloat16 raw[8];
+          *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(h + (size_t)(q0 + x) * width + e);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) v[c] = __bfloat162float(raw[c]);
+        }
+      };
+      for (int k = 0; k < head; ++k) {
+        float x[VT][8];
+#pragma unroll
+        for (int j = 0; j < VT; ++j) input8(k - K + j, x[j]);
+        __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float acc = x[VT - 1][c];
+#pragma unroll
+          for (int j = 0; j < VT; ++j) acc = fmaf(__bfloat162float(w[c * VT + j]), x[j][c], acc);
+          o[c] = __float2bfloat16(acc);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)(q0 + k) * width + e) = *reinterpret_cast<const uint4*>(o);
+      }
+      // the new state, ascending (see below): every place is read before a lower place's write can have reached it
+      for (int k = 0; k < K; ++k) {
+        float v[8];
+        input8(len - K + k, v);
+        *reinterpret_cast<float4*>(st + (size_t)k * width + e) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(st + (size_t)k * width + e + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    }
+  } else {
   for (int e = threadIdx.x; e < width; e += blockDim.x) {
     // input number x of the portion (x < 0: from the state, which holds inputs -K .. -1 at 0 .. K - 1)
     auto input = [&](int x) { return x < 0 ? st[(size_t)(K + x) * width + e] : to_f32<T>(h[(size_t)(q0 + x) * width + e]); };
@@ -183,6 +226,7 @@ __device__ __forceinline__ void causal_conv_token(int t, const T* __restrict__ h
     // the new state: inputs len - K .. len - 1.  Place k takes input len - K + k, which is the old place len + k when that is
     // still a state's input: a place above k, so ascending k reads nothing that was written.
     for (int k = 0; k < K; ++k) st[(size_t)k * width + e] = input(len - K + k);
+  }
   }
 }
 
@@ -206,7 +250,7 @@ IFB_EXPORT int ifb_causal_conv(const void* h, int dtype, const void* weight, int
   if (dtype == IFB_BF16) {
     // rows that read no state go eight channels at a time where the taps are few and everything is aligned
     if (wtype == IFB_BF16 && taps >= 2 && taps <= 8 && width % 8 == 0 && width >= 256 &&
-        (((uintptr_t)h | (uintptr_t)out | (uintptr_t)weight) & 15) == 0) {
+        (((uintptr_t)h | (uintptr_t)out | (uintptr_t)weight | (uintptr_t)state) & 15) == 0) {
 #define CC_VEC(V)                                                                                                              \
   case V:                                                                                                                      \
     return ifb_launch(causal_conv_kernel<__nv_bfloat16, V>, grid, dim3(width >= 2048 ? 256 : 128), 0, stream,                  \

@@ -119,7 +119,7 @@ def test_average_over_depth(K, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,width", [(4, 320), (1, 40), (2, 33), (3, 1000), (6, 64), (16, 8), (5, 2048), (40, 264)])
+@pytest.mark.parametrize("taps,width", [(4, 320), (1, 40), (2, 33), (3, 1000), (6, 64), (16, 8), (5, 2048), (40, 264), (8, 512), (2, 256), (7, 4096)])
 def test_input_convolution_over_steps_and_slots(K, dtype, taps, width):
     """Requests advance by portions of every length around the convolution's reach; what a token sees never depends on the
     cutting: every step's outputs equal the convolution over the whole sequences."""
