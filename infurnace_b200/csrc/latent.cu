@@ -9,10 +9,36 @@
 // The norm in groups of a row that lies in shared memory: out[e] = row[e] * rsqrt(mean over e's group of row^2 + eps) * w[e].
 // Every thread of the block calls it; `scratch` holds 33 floats.
 // ------------------------------------------------------------------------------------------
+template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
 template <typename TO>
 __device__ __forceinline__ void group_norm_row(const float* row, int width, int groups, float eps, const void* weight, int wtype,
                                                TO* out, float* scratch) {
   const int gs = width / groups;
+  if ((gs & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {      // four elements per thread (row is 16-byte aligned)
+    for (int g = 0; g < groups; ++g) {
+      float sq = 0.f;
+      for (int e = threadIdx.x * 4; e < gs; e += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + g * gs + e);
+        sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
+      }
+      const float r = rsqrtf(block_sum(sq, scratch) / (float)gs + eps);
+      for (int e = threadIdx.x * 4; e < gs; e += blockDim.x * 4) {
+        const int i = g * gs + e;
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        store4<TO>(out + i, v.x * r * load_as_f32(weight, wtype, i), v.y * r * load_as_f32(weight, wtype, i + 1),
+                   v.z * r * load_as_f32(weight, wtype, i + 2), v.w * r * load_as_f32(weight, wtype, i + 3));
+      }
+    }
+    return;
+  }
   for (int g = 0; g < groups; ++g) {
     float sq = 0.f;
     for (int e = threadIdx.x; e < gs; e += blockDim.x) { const float v = row[g * gs + e]; sq = fmaf(v, v, sq); }
@@ -28,20 +54,33 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 group_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, float mult, const void* __restrict__ weight, int wtype,
                      int groups, float eps, TO* __restrict__ out, const int* __restrict__ rows, float* __restrict__ keep,
-                     long long keep_stride, int width) {
-  extern __shared__ float gn_row[];
+                     long long keep_stride, int width, int vec) {
+  extern __shared__ __align__(16) float gn_row[];
   __shared__ float scratch[33];
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int b = blockIdx.x;
   const int r = rows ? rows[b] : b;
   float* xr = x + (size_t)r * width;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    float v = xr[e];
-    if (delta) v = fmaf(mult, delta[(size_t)r * width + e], v);
-    gn_row[e] = v;
-    if (delta && !rows) xr[e] = v;
-    if (keep) keep[(size_t)r * keep_stride + e] = v;
+  if (vec) {                                           // width, keep_stride multiples of 4 and every base 16-byte aligned
+    for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + e);
+      if (delta) {
+        const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)r * width + e);
+        v.x = fmaf(mult, d.x, v.x); v.y = fmaf(mult, d.y, v.y); v.z = fmaf(mult, d.z, v.z); v.w = fmaf(mult, d.w, v.w);
+      }
+      *reinterpret_cast<float4*>(gn_row + e) = v;
+      if (delta && !rows) *reinterpret_cast<float4*>(xr + e) = v;
+      if (keep) *reinterpret_cast<float4*>(keep + (size_t)r * keep_stride + e) = v;
+    }
+  } else {
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+      float v = xr[e];
+      if (delta) v = fmaf(mult, delta[(size_t)r * width + e], v);
+      gn_row[e] = v;
+      if (delta && !rows) xr[e] = v;
+      if (keep) keep[(size_t)r * keep_stride + e] = v;
+    }
   }
   __syncthreads();
   group_norm_row<TO>(gn_row, width, groups, eps, weight, wtype, out + (size_t)b * width, scratch);
@@ -54,15 +93,16 @@ IFB_EXPORT int ifb_group_rmsnorm(float* x, const float* delta, float mult, const
   if (width < 1 || groups < 1 || width % groups) return IFB_ERR_SIZE;
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return IFB_ERR_SIZE;
+  const int vec = width % 4 == 0 && keep_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)keep) & 15) == 0;
   if (otype == IFB_BF16) {
     IFB_ALLOW_SMEM(group_rmsnorm_kernel<__nv_bfloat16>, smem);
     return ifb_launch(group_rmsnorm_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, x, delta, mult, weight, wtype, groups,
-                      eps, (__nv_bfloat16*)out, rows, keep, keep_stride, width);
+                      eps, (__nv_bfloat16*)out, rows, keep, keep_stride, width, vec);
   }
   if (otype != IFB_F32) return IFB_ERR_DTYPE;
   IFB_ALLOW_SMEM(group_rmsnorm_kernel<float>, smem);
   return ifb_launch(group_rmsnorm_kernel<float>, dim3(n), dim3(256), smem, stream, x, delta, mult, weight, wtype, groups, eps,
-                    (float*)out, rows, keep, keep_stride, width);
+                    (float*)out, rows, keep, keep_stride, width, vec);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -74,23 +114,45 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 depth_average_kernel(float* __restrict__ x, const float* __restrict__ delta, float mult, float* __restrict__ hist, int slots,
                      int depth, const void* __restrict__ coeff, int ctype, const void* __restrict__ weight, int wtype, int groups,
-                     float eps, TO* __restrict__ out, int width) {
-  extern __shared__ float gn_row[];
+                     float eps, TO* __restrict__ out, int width, int vec) {
+  extern __shared__ __align__(16) float gn_row[];
   __shared__ float scratch[33];
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * width;
   float* hr = hist + (size_t)t * slots * width;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    float v = xr[e];
-    if (delta) v = fmaf(mult, delta[(size_t)t * width + e], v);
-    hr[(size_t)depth * width + e] = v;
-    float acc = 0.f;
-    for (int j = 0; j < depth; ++j) acc = fmaf(load_as_f32(coeff, ctype, j), hr[(size_t)j * width + e], acc);
-    acc = fmaf(load_as_f32(coeff, ctype, depth), v, acc);
-    xr[e] = acc;
-    gn_row[e] = acc;
+  if (vec) {                                           // width a multiple of 4 and every base 16-byte aligned
+    for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + e);
+      if (delta) {
+        const float4 d = *reinterpret_cast<const float4*>(delta + (size_t)t * width + e);
+        v.x = fmaf(mult, d.x, v.x); v.y = fmaf(mult, d.y, v.y); v.z = fmaf(mult, d.z, v.z); v.w = fmaf(mult, d.w, v.w);
+      }
+      *reinterpret_cast<float4*>(hr + (size_t)depth * width + e) = v;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int j = 0; j < depth; ++j) {
+        const float c = load_as_f32(coeff, ctype, j);
+        const float4 u = *reinterpret_cast<const float4*>(hr + (size_t)j * width + e);
+        acc.x = fmaf(c, u.x, acc.x); acc.y = fmaf(c, u.y, acc.y); acc.z = fmaf(c, u.z, acc.z); acc.w = fmaf(c, u.w, acc.w);
+      }
+      const float c = load_as_f32(coeff, ctype, depth);
+      acc.x = fmaf(c, v.x, acc.x); acc.y = fmaf(c, v.y, acc.y); acc.z = fmaf(c, v.z, acc.z); acc.w = fmaf(c, v.w, acc.w);
+      *reinterpret_cast<float4*>(xr + e) = acc;
+      *reinterpret_cast<float4*>(gn_row + e) = acc;
+    }
+  } else {
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+      float v = xr[e];
+      if (delta) v = fmaf(mult, delta[(size_t)t * width + e], v);
+      hr[(size_t)depth * width + e] = v;
+      float acc = 0.f;
+      for (int j = 0; j < depth; ++j) acc = fmaf(load_as_f32(coeff, ctype, j), hr[(size_t)j * width + e], acc);
+      acc = fmaf(load_as_f32(coeff, ctype, depth), v, acc);
+      xr[e] = acc;
+      gn_row[e] = acc;
+    }
   }
   if (out == nullptr) return;
   __syncthreads();
@@ -105,15 +167,16 @@ IFB_EXPORT int ifb_depth_average(float* x, const float* delta, float mult, float
   if (out != nullptr && (groups < 1 || width % groups)) return IFB_ERR_SIZE;
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return IFB_ERR_SIZE;
+  const int vec = width % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)hist) & 15) == 0;
   if (out == nullptr || otype == IFB_F32) {
     IFB_ALLOW_SMEM(depth_average_kernel<float>, smem);
     return ifb_launch(depth_average_kernel<float>, dim3(n), dim3(256), smem, stream, x, delta, mult, hist, slots, depth, coeff,
-                      ctype, weight, wtype, groups, eps, (float*)out, width);
+                      ctype, weight, wtype, groups, eps, (float*)out, width, vec);
   }
   if (otype != IFB_BF16) return IFB_ERR_DTYPE;
   IFB_ALLOW_SMEM(depth_average_kernel<__nv_bfloat16>, smem);
   return ifb_launch(depth_average_kernel<__nv_bfloat16>, dim3(n), dim3(256), smem, stream, x, delta, mult, hist, slots, depth,
-                    coeff, ctype, weight, wtype, groups, eps, (__nv_bfloat16*)out, width);
+                    coeff, ctype, weight, wtype, groups, eps, (__nv_bfloat16*)out, width, vec);
 }
 
 // ------------------------------------------------------------------------------------------
