@@ -92,21 +92,6 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     ke = min(p_hi, kb + per - 1);
   }
   float* my_part = part ? part + ((size_t)(r * gridDim.x + tile_x) * splits + split) * lm_part_floats(RANK) : nullptr;
-  // ---- the rows' queries: [latent-space part | rotated part], bfloat16; two threads per row, a pair of columns at a time
-  {
-    const int row = tid >> 1, rho = row0 + row;
-    const bool live = rho < nrows;
-    const int t = live ? q0 + rho / heads : 0, h = live ? rho % heads : 0;
-    const float* ql = q_lat + ((size_t)h * seg + t) * rank;
-    const float* qr = q_rot + ((size_t)t * heads + h) * rot;
-    bf16* dst = Qs + (size_t)row * LD;
-    for (int c = (tid & 1) * 2; c < KD; c += 4) {
-      float a = 0.f, b = 0.f;
-      if (live && c < rank) { const float2 v = *reinterpret_cast<const float2*>(ql + c); a = v.x; b = v.y; }
-      else if (live && c >= RANK && c - RANK < rot) { const float2 v = *reinterpret_cast<const float2*>(qr + (c - RANK)); a = v.x; b = v.y; }
-      *reinterpret_cast<uint32_t*>(dst + c) = lm_pack(a, b);
-    }
-  }
   const int* table = block_tables + (size_t)r * table_stride;
   // two threads per key: one look at the block table per thread and tile (made one tile ahead, so that no copy waits for
   // it), then 16-byte pieces of the row alternately
@@ -145,6 +130,23 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
   const int ntiles = ke >= kb ? (ke - kb) / LM_KEYS + 1 : 0;
   if (ntiles > 0) load_tile(kb, 0, page_of(kb));
   lm_commit();
+  // ---- the rows' queries: [latent-space part | rotated part], bfloat16; two threads per row, four columns (16 bytes of
+  // float32) at a time, while the first tile of keys is on its way
+  {
+    const int row = tid >> 1, rho = row0 + row;
+    const bool live = rho < nrows;
+    const int t = live ? q0 + rho / heads : 0, h = live ? rho % heads : 0;
+    const float* ql = q_lat + ((size_t)h * seg + t) * rank;
+    const float* qr = q_rot + ((size_t)t * heads + h) * rot;
+    bf16* dst = Qs + (size_t)row * LD;
+#pragma unroll 6
+    for (int c = (tid & 1) * 4; c < KD; c += 8) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live && c < rank) v = *reinterpret_cast<const float4*>(ql + c);
+      else if (live && c >= RANK && c - RANK < rot) v = *reinterpret_cast<const float4*>(qr + (c - RANK));
+      *reinterpret_cast<uint2*>(dst + c) = make_uint2(lm_pack(v.x, v.y), lm_pack(v.z, v.w));
+    }
+  }
   int page_next = ntiles > 1 ? page_of(kb + LM_KEYS) : 0;
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) load_tile(kb + (it + 1) * LM_KEYS, (it + 1) & 1, page_next);
@@ -339,7 +341,7 @@ IFB_EXPORT int ifb_latent_attention_mma(const float* q_lat, const float* q_rot, 
                                         int rank, int rot, float scale, int window, int splits, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return IFB_OK;
   if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 || splits > 32 ||
-      (splits > 1 && part == nullptr))
+      (splits > 1 && part == nullptr) || (((uintptr_t)q_lat | (uintptr_t)q_rot) & 15))      // queries are read 16 bytes at a time
     return IFB_ERR_SIZE;
 #define LM_ARGS                                                                                                                \
   q_lat, q_rot, seg, lat_pages, rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, out, part, requests, \
