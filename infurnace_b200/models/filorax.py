@@ -46,7 +46,7 @@ def _mlp(mlp, p, W):
     return RoutedExpertsSpec(
         W, mlp["expert"]["ff"], router["top"], EXPERT_ACTIVATION, p + "router",
         tuple((f"{p}e{j}.gate", f"{p}e{j}.up", f"{p}e{j}.down") for j in range(router["experts"])),
-        scoring="all", weight_scale=float(router.get("scale", 1.0)),
+        scoring="all", weight_scale=float(router["scale"]) if router.get("scale") is not None else 1.0,
         groups=(int(groups["count"]), int(groups["keep"])) if groups else None,
         shared=GatedMLPSpec(W, shared["ff"], EXPERT_ACTIVATION, p + "shared.gate", p + "shared.up", p + "shared.down") if shared else None,
         shared_gate=p + "shared.sg" if shared else None)
