@@ -120,11 +120,18 @@ class RotarySpec:
 
     ``interleaved`` False pairs element i with i + rotary_dim/2 (the half-split form
     of model.py:24-27); True pairs 2i with 2i+1.  ``theta`` is the base of the
-    frequencies inv_freq_i = theta^(-2i/rotary_dim) (model.py:18-22)."""
+    frequencies inv_freq_i = theta^(-2i/rotary_dim) (model.py:18-22).
+
+    ``scaling`` = (factor, original, fast, slow) stretches the slow frequencies (YaRN): with
+    d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
+    turns at inv_freq_i / factor * ramp_i + inv_freq_i * (1 - ramp_i), and cosine and sine are both
+    multiplied by 0.1 * ln(factor) + 1."""
     head_dim: int
     rotary_dim: int
     theta: float
     interleaved: bool = False
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         return {}
@@ -192,16 +199,23 @@ class GatedMLPSpec:
 
 @dataclass(frozen=True)
 class PreNormBlockSpec:
-    """x += mixer(norm1(x)); x += ffn(norm2(x))  (model.py:101,143,145,148)."""
+    """x += mixer(norm1(x)); x += ffn(norm2(x))  (model.py:101,143,145,148).  ``ffn`` None: the block has no
+    feed-forward (``ffn_norm`` is then None too, and ``unused`` may name norm weights that a folder stores all the
+    same).  ``side``: a per-layer token input (a ``TokenSideSpec``) that follows the feed-forward."""
     mixer_norm: object
     mixer: object
-    ffn_norm: object
-    ffn: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    side: Optional[object] = None
+    unused: Tuple[Tuple[str, int], ...] = ()      # (name, length) of vectors a folder may hold that no part reads
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         t = {}
-        for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn):
-            t.update(part.tensors())
+        for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.side):
+            if part is not None:
+                t.update(part.tensors())
+        for name, size in self.unused:
+            t.setdefault(name, TensorSpec((size,), optional=True))
         return t
 
     def cache_need(self):
@@ -529,12 +543,55 @@ class GatedUnitSpec:
 
 
 @dataclass(frozen=True)
+class RealGatedRecurrenceSpec:
+    """The recurrent block around a real-gated linear recurrent unit (RG-LRU).  Two branches of ``width`` channels:
+    y = gelu_tanh(``y_proj`` h + ``y_bias``) and u = conv(``x_proj`` h + ``x_bias``), a causal convolution per channel
+    over time (``conv`` [width, taps], the last column is the current token's, zeros before the start, plus
+    ``conv_bias``; no activation).  u in ``blocks`` equal parts: r = sigmoid(``a_gate``[b] u_b + ``a_bias``[b]),
+    i = sigmoid(``x_gate``[b] u_b + ``x_bias_gate``[b]) with square matrices [out, in] per part.
+    log a = -``decay_scale`` * r * softplus(``decay``); S <- a S + sqrt(1 - a^2) * i * u per channel of a float32 state
+    that starts at zero; the output is ``o_proj``(S * y).  The convolution's last taps - 1 inputs are state too."""
+    hidden_size: int
+    width: int
+    blocks: int
+    taps: int
+    decay_scale: float
+    y_proj: str
+    y_bias: str
+    x_proj: str
+    x_bias: str
+    conv: str
+    conv_bias: str
+    a_gate: str
+    a_bias: str
+    x_gate: str
+    x_bias_gate: str
+    decay: str
+    o_proj: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        n, W, B = self.width, self.hidden_size, self.blocks
+        bs = n // B
+        return {self.y_proj: TensorSpec((n, W)), self.y_bias: TensorSpec((n,), init=(0.0, 0.3)),
+                self.x_proj: TensorSpec((n, W)), self.x_bias: TensorSpec((n,), init=(0.0, 0.3)),
+                self.conv: TensorSpec((n, self.taps), init=(0.0, 0.4)), self.conv_bias: TensorSpec((n,), init=(0.0, 0.3)),
+                self.a_gate: TensorSpec((B, bs, bs), init=(0.0, 0.2)), self.a_bias: TensorSpec((B, bs), init=(0.0, 0.5)),
+                self.x_gate: TensorSpec((B, bs, bs), init=(0.0, 0.2)), self.x_bias_gate: TensorSpec((B, bs), init=(0.0, 0.5)),
+                self.decay: TensorSpec((n,), init=(0.0, 1.0)), self.o_proj: TensorSpec((W, n))}
+
+    def cache_need(self):
+        """Entry 0: the recurrence's state; entry 1: the convolution's last inputs."""
+        return (StateNeed((self.width,)), StateNeed((max(self.taps - 1, 1), self.width)))
+
+
+@dataclass(frozen=True)
 class RotaryValueAttentionSpec:
     """Grouped-query softmax attention whose values carry positions too.  q and k are rotated on their first
     ``position.rotary_dim`` entries (:class:`RotarySpec`).  ``value_norm``: each value head is divided by its root
     mean square (no weight) before it is cached.  ``value_position``: the value of position j is rotated by j over
     that description's width before it is cached, and each head's summed output at position i is rotated back by
-    -i.  Causal, optional window, plain softmax; key and value heads may differ in width."""
+    -i.  Causal, optional window, plain softmax; key and value heads may differ in width.  ``v_proj`` None: the
+    values are the keys as projected, before their rotation, and the model has no v matrix."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -544,7 +601,7 @@ class RotaryValueAttentionSpec:
     eps: float
     q_proj: str
     k_proj: str
-    v_proj: str
+    v_proj: Optional[str]
     o_proj: str
     position: Optional[RotarySpec] = None
     value_norm: bool = False
@@ -553,10 +610,12 @@ class RotaryValueAttentionSpec:
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         W = self.hidden_size
-        return {self.q_proj: TensorSpec((self.num_heads * self.head_dim, W)),
-                self.k_proj: TensorSpec((self.num_kv_heads * self.head_dim, W)),
-                self.v_proj: TensorSpec((self.num_kv_heads * self.value_head_dim, W)),
-                self.o_proj: TensorSpec((W, self.num_heads * self.value_head_dim))}
+        t = {self.q_proj: TensorSpec((self.num_heads * self.head_dim, W)),
+             self.k_proj: TensorSpec((self.num_kv_heads * self.head_dim, W)),
+             self.o_proj: TensorSpec((W, self.num_heads * self.value_head_dim))}
+        if self.v_proj is not None:
+            t[self.v_proj] = TensorSpec((self.num_kv_heads * self.value_head_dim, W))
+        return t
 
     def cache_need(self):
         return KVCacheNeed(self.num_kv_heads, self.head_dim, self.window,
@@ -587,7 +646,10 @@ class RoutedExpertsSpec:
 
     ``scoring`` "chosen" (the default): each token runs the ``top`` experts with the largest logits, weighted by the
     softmax over those logits only.  ``scoring`` "all": the scores are the softmax over all experts, the ``top`` largest
-    scores are chosen and the weights are those scores times ``weight_scale``, not renormalised.  ``groups`` =
+    scores are chosen and the weights are those scores times ``weight_scale``, not renormalised.  ``scoring`` "sigmoid":
+    the scores are sigmoid(z) per expert, chosen and weighted like "all".  ``weight_on`` "output" (the default): the
+    weight multiplies the expert's result; "input": it multiplies what the expert reads, and the results are summed as
+    they are (the two differ because an expert is not linear).  ``groups`` =
     (count, keep): the experts form ``count`` equal groups of neighbours, a group's score is its largest score, and only
     experts of the ``keep`` best groups can be chosen (None: no such limit).  ``shared``: a gated feed-forward that
     every token runs, added to the sum; with ``shared_gate`` (a tensor [1, hidden]) it is first multiplied by
@@ -603,6 +665,7 @@ class RoutedExpertsSpec:
     groups: Optional[Tuple[int, int]] = None
     shared: Optional[GatedMLPSpec] = None
     shared_gate: Optional[str] = None
+    weight_on: str = "output"
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         t = {self.router: TensorSpec((len(self.experts), self.hidden_size), init=(0.0, 0.3))}
@@ -708,7 +771,9 @@ class LatentAttentionSpec:
     ``position`` (a :class:`RotarySpec` over the rot_dim part) turns the rotated parts of q and of the key by the token's
     position.  ``window`` w: position i sees j with 0 <= i - j < w (None: every j <= i).  ``sink``: a tensor [heads]; exp
     of it joins the softmax's denominator, with no key and no value.  ``gate``: the heads side by side are multiplied by
-    sigmoid(G h) before ``o_proj``."""
+    sigmoid(G h) before ``o_proj``; with ``gate_per_head`` G has one row per head and the whole head takes one number.
+    ``q_rank`` r: the queries go through a latent of their own, q = ``q_proj`` (rmsnorm(``q_down`` h) * ``q_norm``),
+    with ``q_down`` [r, hidden], ``q_norm`` [r] and ``q_proj`` [heads * (head_dim + rot_dim), r]."""
     hidden_size: int
     num_heads: int
     head_dim: int
@@ -727,10 +792,14 @@ class LatentAttentionSpec:
     window: Optional[int] = None
     sink: Optional[str] = None
     gate: Optional[str] = None
+    gate_per_head: bool = False
+    q_rank: Optional[int] = None
+    q_down: Optional[str] = None
+    q_norm: Optional[str] = None
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         W, H = self.hidden_size, self.num_heads
-        t = {self.q_proj: TensorSpec((H * (self.head_dim + self.rot_dim), W)),
+        t = {self.q_proj: TensorSpec((H * (self.head_dim + self.rot_dim), self.q_rank or W)),
              self.down_proj: TensorSpec((self.kv_rank + self.rot_dim, W)),
              self.latent_norm: TensorSpec((self.kv_rank,)),
              self.k_up: TensorSpec((H * self.head_dim, self.kv_rank)),
@@ -739,7 +808,10 @@ class LatentAttentionSpec:
         if self.sink is not None:
             t[self.sink] = TensorSpec((H,), init=(0.0, 1.0))
         if self.gate is not None:
-            t[self.gate] = TensorSpec((H * self.value_head_dim, W))
+            t[self.gate] = TensorSpec((H if self.gate_per_head else H * self.value_head_dim, W))
+        if self.q_rank:
+            t[self.q_down] = TensorSpec((self.q_rank, W))
+            t[self.q_norm] = TensorSpec((self.q_rank,))
         return t
 
     def cache_need(self):

@@ -2,7 +2,8 @@
 //
 // (1) rotary_store: per token, the q and k heads are rotated on their first rot_dims entries by the token's angles,
 // each value head is divided by its root mean square (optional) and rotated over its whole width by the token's
-// angles (optional); q goes to a row buffer, k and v into their page streams at the token's slot.  The angles come
+// angles (optional); q goes to a row buffer, k and v into their page streams at the token's slot.  Where a model has no
+// value projection the values are the key heads as projected, before their rotation.  The angles come
 // as a table of (cos, sin) pairs per token, float32.  A rotation pairs entry m with m + dims/2, or 2m with 2m + 1
 // when interleaved; the pair (u, v) becomes (u c - v s, v c + u s).
 //
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(128)
 rotary_store_kernel(const float* __restrict__ qkv, int ld, int H, int G, int d, int dv, const float* __restrict__ qk_table,
                     int rot_dims, int interleaved, int v_norm, float v_eps, const float* __restrict__ v_table, int v_interleaved,
                     T* __restrict__ q_out, T* __restrict__ k_pages, long long k_page_stride, T* __restrict__ v_pages,
-                    long long v_page_stride, const int* __restrict__ slot_mapping, int page_size) {
+                    long long v_page_stride, const int* __restrict__ slot_mapping, int page_size, int v_from_k) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int n = blockIdx.x;
@@ -57,7 +58,8 @@ rotary_store_kernel(const float* __restrict__ qkv, int ld, int H, int G, int d, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const float* vt = v_table ? v_table + (size_t)n * dv : nullptr;
   for (int g = warp; g < G; g += warps) {
-    const float* v = row + (size_t)(H + G) * d + (size_t)g * dv;
+    // v_from_k: the row holds no values; a value head is the key head as projected, before its rotation (dv == d)
+    const float* v = v_from_k ? row + (size_t)(H + g) * d : row + (size_t)(H + G) * d + (size_t)g * dv;
     float gain = 1.f;
     if (v_norm) {
       float ss = 0.f;
@@ -72,18 +74,18 @@ rotary_store_kernel(const float* __restrict__ qkv, int ld, int H, int G, int d, 
 IFB_EXPORT int ifb_rotary_store(const float* qkv, int ld, int H, int G, int d, int dv, const float* qk_table, int rot_dims,
                                 int interleaved, int v_norm, float v_eps, const float* v_table, int v_interleaved, void* q_out,
                                 int dtype, void* k_pages, long long k_page_stride, void* v_pages, long long v_page_stride,
-                                const int* slot_mapping, int page_size, int n, cudaStream_t stream) {
+                                const int* slot_mapping, int page_size, int n, int v_from_k, cudaStream_t stream) {
   if (n <= 0) return IFB_OK;
-  if (H < 1 || G < 1 || d < 1 || dv < 1 || page_size < 1) return IFB_ERR_SIZE;
+  if (H < 1 || G < 1 || d < 1 || dv < 1 || page_size < 1 || (v_from_k && dv != d)) return IFB_ERR_SIZE;
   if ((qk_table && (rot_dims < 2 || rot_dims % 2 || rot_dims > d)) || (v_table && dv % 2)) return IFB_ERR_ARG;
   if (dtype == IFB_BF16)
     return ifb_launch(rotary_store_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, qkv, ld, H, G, d, dv, qk_table, rot_dims,
                       interleaved, v_norm, v_eps, v_table, v_interleaved, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages,
-                      k_page_stride, (__nv_bfloat16*)v_pages, v_page_stride, slot_mapping, page_size);
+                      k_page_stride, (__nv_bfloat16*)v_pages, v_page_stride, slot_mapping, page_size, v_from_k);
   if (dtype != IFB_F32) return IFB_ERR_DTYPE;
   return ifb_launch(rotary_store_kernel<float>, dim3(n), dim3(128), 0, stream, qkv, ld, H, G, d, dv, qk_table, rot_dims, interleaved,
                     v_norm, v_eps, v_table, v_interleaved, (float*)q_out, (float*)k_pages, k_page_stride, (float*)v_pages,
-                    v_page_stride, slot_mapping, page_size);
+                    v_page_stride, slot_mapping, page_size, v_from_k);
 }
 
 // rows[n][head][:] are rotated in place by the token's angles, forward (sign 1) or back (sign -1), over `dims` entries

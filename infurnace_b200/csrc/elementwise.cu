@@ -191,26 +191,26 @@ IFB_EXPORT int ifb_rmsnorm(float* x, const float* delta, int num_splits, long lo
 }
 
 // ------------------------------------------------------------------------------------------
-// rope_table: table[tok][i] = (cos, sin)(positions[tok] * inv_freq[i]), i < half.  A step computes it once and
+// rope_table: table[tok][i] = gain * (cos, sin)(positions[tok] * inv_freq[i]), i < half.  A step computes it once and
 // every layer's rotation reads it (the angles do not depend on the layer).
 // ------------------------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half,
-                                  float2* __restrict__ table, int n_tokens) {
+                                  float2* __restrict__ table, int n_tokens, float gain) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_tokens * half) return;
   float s, c;
   sincosf((float)positions[idx / half] * inv_freq[idx % half], &s, &c);
-  table[idx] = make_float2(c, s);
+  table[idx] = make_float2(c * gain, s * gain);
 }
 
-IFB_EXPORT int ifb_rope_table(const int* positions, const float* inv_freq, int half, float* table, int n_tokens,
+IFB_EXPORT int ifb_rope_table(const int* positions, const float* inv_freq, int half, float* table, int n_tokens, float gain,
                               cudaStream_t stream) {
   if (n_tokens <= 0 || half <= 0) return IFB_OK;
   const long long total = (long long)n_tokens * half;
   return ifb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, positions, inv_freq, half,
-                    reinterpret_cast<float2*>(table), n_tokens);
+                    reinterpret_cast<float2*>(table), n_tokens, gain);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -347,7 +347,8 @@ latent_prepare_kernel(const float* __restrict__ proj, long long stride, int head
                       const void* __restrict__ norm_w, int wtype, float eps, const float* __restrict__ table, int dims,
                       TA* __restrict__ q_plain, int seg, float* __restrict__ q_rot, TC* __restrict__ latent_pages,
                       TC* __restrict__ rot_pages, const int* __restrict__ slot_mapping, int* __restrict__ offsets,
-                      int* __restrict__ tile_head, int tile, int tokens) {
+                      int* __restrict__ tile_head, int tile, int tokens, const float* __restrict__ q_rows, long long q_stride,
+                      int interleaved) {
   __shared__ float scratch[33];
   ifb_pdl_wait();
   ifb_pdl_trigger();
@@ -360,6 +361,7 @@ latent_prepare_kernel(const float* __restrict__ proj, long long stride, int head
     }
   }
   const float* row = proj + (size_t)t * stride;
+  const float* qrow = q_rows ? q_rows + (size_t)t * q_stride : row;        // the queries may come from a product of their own
   const float* tab = table ? table + (size_t)t * dims : nullptr;
   const int half = dims / 2;
   // queries
@@ -367,14 +369,17 @@ latent_prepare_kernel(const float* __restrict__ proj, long long stride, int head
   for (int i = threadIdx.x; i < heads * qw; i += blockDim.x) {
     const int h = i / qw, c = i - h * qw;
     if (c < dim) {
-      q_plain[((size_t)h * seg + t) * dim + c] = from_f32<TA>(row[i]);
+      q_plain[((size_t)h * seg + t) * dim + c] = from_f32<TA>(qrow[i]);
     } else {
       const int d = c - dim;
-      float v = row[i];
+      float v = qrow[i];
       if (tab != nullptr && d < dims) {
-        const int p = d < half ? d : d - half;
+        // the pair (u, v) becomes (u c - v s, v c + u s): entries m and m + dims/2, or 2m and 2m + 1 when interleaved
+        const bool lead = interleaved ? !(d & 1) : d < half;
+        const int p = interleaved ? d >> 1 : (lead ? d : d - half);
+        const int other = interleaved ? (lead ? 1 : -1) : (lead ? half : -half);
         const float cs = tab[2 * p], sn = tab[2 * p + 1];
-        v = d < half ? v * cs - row[i + half] * sn : v * cs + row[i - half] * sn;
+        v = lead ? v * cs - qrow[i + other] * sn : v * cs + qrow[i + other] * sn;
       }
       q_rot[((size_t)t * heads + h) * rot + d] = v;
     }
@@ -393,9 +398,11 @@ latent_prepare_kernel(const float* __restrict__ proj, long long stride, int head
   for (int d = threadIdx.x; d < rot; d += blockDim.x) {
     float v = kr[d];
     if (tab != nullptr && d < dims) {
-      const int p = d < half ? d : d - half;
+      const bool lead = interleaved ? !(d & 1) : d < half;
+      const int p = interleaved ? d >> 1 : (lead ? d : d - half);
+      const int other = interleaved ? (lead ? 1 : -1) : (lead ? half : -half);
       const float cs = tab[2 * p], sn = tab[2 * p + 1];
-      v = d < half ? v * cs - kr[d + half] * sn : v * cs + kr[d - half] * sn;
+      v = lead ? v * cs - kr[d + other] * sn : v * cs + kr[d + other] * sn;
     }
     rot_pages[(size_t)slot * rot + d] = from_f32<TC>(v);
   }
@@ -404,7 +411,8 @@ latent_prepare_kernel(const float* __restrict__ proj, long long stride, int head
 IFB_EXPORT int ifb_latent_prepare(const float* proj, long long stride, int heads, int dim, int rot, int rank, int down_col,
                                   const void* norm_w, int wtype, float eps, const float* table, int dims, void* q_plain, int atype,
                                   int seg, float* q_rot, void* latent_pages, void* rot_pages, int ctype, const int* slot_mapping,
-                                  int* offsets, int* tile_head, int tile, int tokens, cudaStream_t stream) {
+                                  int* offsets, int* tile_head, int tile, int tokens, const float* q_rows, long long q_stride,
+                                  int interleaved, cudaStream_t stream) {
   if (tokens <= 0) return IFB_OK;
   if (heads < 1 || dim < 1 || rot < 0 || rank < 1 || seg < tokens || dims < 0 || dims > rot || (dims & 1)) return IFB_ERR_SIZE;
   if (tile_head != nullptr && (tile < 1 || seg % tile)) return IFB_ERR_SIZE;
@@ -412,7 +420,7 @@ IFB_EXPORT int ifb_latent_prepare(const float* proj, long long stride, int heads
 #define LP_LAUNCH(TA, TC)                                                                                                        \
   return ifb_launch(latent_prepare_kernel<TA, TC>, dim3(tokens), dim3(256), 0, stream, proj, stride, heads, dim, rot, rank,      \
                     down_col, norm_w, wtype, eps, table, dims, (TA*)q_plain, seg, q_rot, (TC*)latent_pages, (TC*)rot_pages,      \
-                    slot_mapping, offsets, tile_head, tile, tokens)
+                    slot_mapping, offsets, tile_head, tile, tokens, q_rows, q_stride, interleaved)
   if (atype == IFB_BF16) LP_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   if (atype == IFB_F32) LP_LAUNCH(float, float);
 #undef LP_LAUNCH
@@ -420,32 +428,33 @@ IFB_EXPORT int ifb_latent_prepare(const float* proj, long long stride, int heads
 }
 
 // ------------------------------------------------------------------------------------------
-// out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (gate null: no gate): from the head-major result of a
+// out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (gate null: no gate; per_head: gate[t, h], one number for
+// the whole head): from the head-major result of a
 // grouped product (float32, `seg` rows per head) to the rows the output product reads.
 // ------------------------------------------------------------------------------------------
 template <typename TO>
 __global__ void __launch_bounds__(256)
 gate_heads_kernel(const float* __restrict__ y, int seg, const float* __restrict__ gate, long long gate_stride,
-                  TO* __restrict__ out, int heads, int vdim) {
+                  TO* __restrict__ out, int heads, int vdim, int per_head) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int t = blockIdx.x, width = heads * vdim;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const int h = i / vdim, v = i - h * vdim;
     float val = y[((size_t)h * seg + t) * vdim + v];
-    if (gate != nullptr) val *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + i]));
+    if (gate != nullptr) val *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + (per_head ? h : i)]));
     out[(size_t)t * width + i] = from_f32<TO>(val);
   }
 }
 
 IFB_EXPORT int ifb_gate_heads(const float* y, int seg, const float* gate, long long gate_stride, void* out, int otype, int tokens,
-                              int heads, int vdim, cudaStream_t stream) {
+                              int heads, int vdim, int per_head, cudaStream_t stream) {
   if (tokens <= 0) return IFB_OK;
   if (heads < 1 || vdim < 1 || seg < tokens) return IFB_ERR_SIZE;
   if (otype == IFB_BF16)
     return ifb_launch(gate_heads_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, y, seg, gate, gate_stride,
-                      (__nv_bfloat16*)out, heads, vdim);
+                      (__nv_bfloat16*)out, heads, vdim, per_head);
   if (otype != IFB_F32) return IFB_ERR_DTYPE;
   return ifb_launch(gate_heads_kernel<float>, dim3(tokens), dim3(256), 0, stream, y, seg, gate, gate_stride, (float*)out, heads,
-                    vdim);
+                    vdim, per_head);
 }

@@ -10,7 +10,8 @@
 // ids[n][j], j < top: the indices of row n's `top` largest scores, largest first, the lower index among equals.
 // mode 0: the scores are the logits, and gates[n][j] is the softmax over the chosen logits only.  mode 1: the scores are
 // the softmax over all experts, only experts of the `keep` groups (of `groups` equal groups of neighbours) whose best score
-// is largest can be chosen, and gates[n][j] = score * wscale, not renormalised.  A row of logits has `stride` entries, of
+// is largest can be chosen, and gates[n][j] = score * wscale, not renormalised.  mode 2: the scores are sigmoid(logit) per
+// expert (the order of the logits is the order of the scores), gates[n][j] = score * wscale.  A row of logits has `stride` entries, of
 // which the first `experts` are the router's.  A warp per row; a lane holds the logits e = lane, lane + 32, ... (up to
 // MR_PER_LANE * 32 experts); lane j keeps the j-th chosen score (up to 32 choices).
 // ------------------------------------------------------------------------------------------
@@ -98,6 +99,10 @@ __device__ __forceinline__ void mr_route_row(const float* __restrict__ logits, i
     if (lane < top) gates[(size_t)row * top + lane] = mine * md.wscale;
     return;
   }
+  if (md.mode == 2) {
+    if (lane < top) gates[(size_t)row * top + lane] = md.wscale / (1.f + expf(-mine));
+    return;
+  }
   const float p = lane < top ? expf(mine - first) : 0.f;
   sum = warp_sum(p);
   if (lane < top) gates[(size_t)row * top + lane] = p / sum;
@@ -141,7 +146,7 @@ moe_route_plan_small_kernel(const float* __restrict__ logits, int* __restrict__ 
 }
 
 static bool mr_mode_ok(const MrMode& md, int experts) {
-  return md.stride >= experts && (md.mode == 0 || md.mode == 1) && md.groups >= 1 && md.keep >= 1 && md.keep <= md.groups &&
+  return md.stride >= experts && md.mode >= 0 && md.mode <= 2 && md.groups >= 1 && md.keep >= 1 && md.keep <= md.groups &&
          experts % md.groups == 0;
 }
 
@@ -305,6 +310,56 @@ IFB_EXPORT int ifb_moe_gather_rows(const void* x, const int* perm, int top, cons
   if (((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return IFB_ERR_ALIGN;
   return ifb_launch(moe_gather_rows_kernel, dim3(places), dim3(128), 0, stream, (const uint4*)x, perm, top, tile_expert, pad,
                     (uint4*)out, k / 8);
+}
+
+// out[place][:] = gates[perm[place]] * x[perm[place] / top][:] in out's dtype (the product in float32, rounded once): what an
+// expert reads when its weight multiplies its input.  Zeros where perm[place] < 0; with tile_expert, places of unused tiles
+// are left alone.  Any dtype and width; bfloat16 rows of a multiple of 8 elements go 16 bytes at a time.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_scaled_kernel(const T* __restrict__ x, const int* __restrict__ perm, int top, const float* __restrict__ gates,
+                         const int* __restrict__ tile_expert, int pad, T* __restrict__ out, int k, int vec) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int place = blockIdx.x;
+  if (tile_expert != nullptr && tile_expert[place / pad] < 0) return;
+  const int p = perm[place];
+  T* dst = out + (size_t)place * k;
+  if (p < 0) {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+    return;
+  }
+  const float g = gates[p];
+  const T* src = x + (size_t)(p / top) * k;
+  if constexpr (sizeof(T) == 2) {
+    if (vec) {
+      for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {
+        uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          h2[j] = __floats2bfloat162_rn(f.x * g, f.y * g);
+        }
+        *reinterpret_cast<uint4*>(dst + i) = raw;
+      }
+      return;
+    }
+  }
+  for (int i = threadIdx.x; i < k; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(src[i]) * g);
+}
+
+IFB_EXPORT int ifb_moe_gather_scaled(const void* x, int dtype, const int* perm, int top, const float* gates, const int* tile_expert,
+                                     int pad, void* out, int places, int k, cudaStream_t stream) {
+  if (places <= 0) return IFB_OK;
+  if (k < 1 || top < 1 || pad < 1) return IFB_ERR_SIZE;
+  const int vec = k % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+  if (dtype == IFB_BF16)
+    return ifb_launch(moe_gather_scaled_kernel<__nv_bfloat16>, dim3(places), dim3(128), 0, stream, (const __nv_bfloat16*)x, perm, top,
+                      gates, tile_expert, pad, (__nv_bfloat16*)out, k, vec);
+  if (dtype != IFB_F32) return IFB_ERR_DTYPE;
+  return ifb_launch(moe_gather_scaled_kernel<float>, dim3(places), dim3(128), 0, stream, (const float*)x, perm, top, gates,
+                    tile_expert, pad, (float*)out, k, 0);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -693,7 +748,8 @@ IFB_EXPORT int ifb_moe_linear(const void* x, int x_dtype, const void* w, int w_d
 }
 
 // ------------------------------------------------------------------------------------------
-// out[n][f] = sum_j gates[n][j] * y[pos[n * top + j]][f], j ascending, float32; then, with `shared` (the result of an
+// out[n][f] = sum_j gates[n][j] * y[pos[n * top + j]][f], j ascending, float32 (gates null: every weight is 1, for experts whose
+// weight went into what they read); then, with `shared` (the result of an
 // expert that every row runs), + g * shared[n][f], g = sigmoid(shared_logit[n * logit_stride]) or 1 without a logit.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -708,7 +764,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, con
   for (int f = threadIdx.x; f < width; f += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
-      acc = fmaf(gates[(size_t)n * top + j], y[(size_t)pos[(size_t)n * top + j] * width + f], acc);
+      acc = fmaf(gates ? gates[(size_t)n * top + j] : 1.f, y[(size_t)pos[(size_t)n * top + j] * width + f], acc);
     if (shared != nullptr) acc = fmaf(g, shared[(size_t)n * width + f], acc);
     out[(size_t)n * width + f] = acc;
   }

@@ -1,0 +1,219 @@
+// The recurrent block around a real-gated linear recurrent unit (RG-LRU), after its two input projections:
+//
+// (1) rglru_conv: u_t = conv_b + sum_(j <= K) w[:, j] * xin_(t - K + j), K = taps - 1, xin = x_raw + x_bias, per channel over
+// each request's tokens in order, zeros before a sequence's start.  The K inputs before a portion come from the request's
+// state [slots, max(K, 1), width] (float32, oldest first), which then takes the portion's last K inputs.  u is written
+// twice: token-major in float32 (the recurrence reads it) and block-major [blocks, seg, width / blocks] in the products'
+// dtype (the block-diagonal gate products read it as a grouped product, a block being what an expert is there).
+//
+// (2) rglru_scan: per channel of a float32 state, r = sigmoid(gr + a_bias), i = sigmoid(gi + i_bias) from the gate products'
+// float32 results (block-major rows of [r | i]), log a = -scale * r * softplus(lam), a = exp(log a),
+// S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu_tanh(y_raw + y_bias).  A thread owns a (request, channel) and walks the
+// request's tokens of the step from the slot's state.  Long portions are cut into chunks of 64 tokens that run side by
+// side in two launches: the first forms every chunk's map S -> A S + B from zero and sets the slot's state aside, the
+// second folds the maps of the chunks before its own onto that state, walks its chunk and writes the outputs (the last
+// chunk of a request writes the state).  The two forms differ by rounding only.  Everything here is float32 arithmetic.
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------ the convolution
+template <typename TB>
+__global__ void __launch_bounds__(128)
+rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const float* __restrict__ x_bias,
+                  const float* __restrict__ conv_w, const float* __restrict__ conv_b, float* __restrict__ state,
+                  const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                  const int* __restrict__ req_index, float* __restrict__ u, TB* __restrict__ ub, int seg, int blocks,
+                  int* __restrict__ offsets, int* __restrict__ tile_block, int tile, int width, int taps) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int t = blockIdx.x;
+  if (t == 0) {
+    for (int b = threadIdx.x; b <= blocks; b += blockDim.x) offsets[b] = b * seg;
+    if (tile_block != nullptr) {
+      const int per = seg / tile;
+      for (int j = threadIdx.x; j < blocks * per; j += blockDim.x) tile_block[j] = j / per;
+    }
+  }
+  const int bs = width / blocks;
+  const int r = req_index[t];
+  const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
+  if (seq_lens[r] <= 0) {                              // a padding row of a recorded step: it stores and sees nothing
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+      u[(size_t)t * width + e] = 0.f;
+      ub[((size_t)(e / bs) * seg + t) * bs + e % bs] = from_f32<TB>(0.f);
+    }
+    return;
+  }
+  const int K = taps - 1, Kp = K > 0 ? K : 1;
+  if (i > 0 && i < K) return;                          // the block of the portion's first token computes these
+  float* st = state + (size_t)state_slots[r] * Kp * width;
+  const float* xr = proj + x_col;
+  // input idx of the portion (negative: from the state), channel e
+  auto input = [&](int idx, int e) -> float {
+    return idx >= 0 ? xr[(size_t)(q0 + idx) * ld + e] + x_bias[e] : st[(size_t)(K + idx) * width + e];
+  };
+  auto token = [&](int ii, int e) {
+    float acc = conv_b[e];
+    for (int j = 0; j <= K; ++j) acc = fmaf(conv_w[(size_t)e * taps + j], input(ii - K + j, e), acc);
+    u[(size_t)(q0 + ii) * width + e] = acc;
+    ub[((size_t)(e / bs) * seg + q0 + ii) * bs + e % bs] = from_f32<TB>(acc);
+  };
+  if (i >= K) {                                        // reads this step's rows only
+    for (int e = threadIdx.x; e < width; e += blockDim.x) token(i, e);
+    return;
+  }
+  // i == 0 and K > 0: the tokens that read the state, then the state's replacement; a channel is one thread's throughout
+  const int lim = len < K ? len : K;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    for (int ii = 0; ii < lim; ++ii) token(ii, e);
+    for (int k = 0; k < K; ++k) {                      // new entry k is the input at portion index len - K + k
+      const int src = len - K + k;
+      st[(size_t)k * width + e] = src >= 0 ? xr[(size_t)(q0 + src) * ld + e] + x_bias[e] : st[(size_t)(k + len) * width + e];
+    }
+  }
+}
+
+IFB_EXPORT int ifb_rglru_conv(const float* proj, long long ld, int x_col, const float* x_bias, const float* conv_w,
+                              const float* conv_b, float* state, const int* state_slots, const int* cu_q, const int* seq_lens,
+                              const int* req_index, float* u, void* ub, int ub_dtype, int seg, int blocks, int* offsets,
+                              int* tile_block, int tile, int n, int width, int taps, cudaStream_t stream) {
+  if (n <= 0) return IFB_OK;
+  if (width < 1 || blocks < 1 || width % blocks || taps < 1 || seg < n || x_col < 0 || x_col + width > ld) return IFB_ERR_SIZE;
+  if (tile_block != nullptr && (tile < 1 || seg % tile)) return IFB_ERR_SIZE;
+  if (ub_dtype == IFB_BF16)
+    return ifb_launch(rglru_conv_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, proj, ld, x_col, x_bias, conv_w, conv_b,
+                      state, state_slots, cu_q, seq_lens, req_index, u, (__nv_bfloat16*)ub, seg, blocks, offsets, tile_block,
+                      tile, width, taps);
+  if (ub_dtype != IFB_F32) return IFB_ERR_DTYPE;
+  return ifb_launch(rglru_conv_kernel<float>, dim3(n), dim3(128), 0, stream, proj, ld, x_col, x_bias, conv_w, conv_b, state,
+                    state_slots, cu_q, seq_lens, req_index, u, (float*)ub, seg, blocks, offsets, tile_block, tile, width, taps);
+}
+
+// ------------------------------------------------------------------------------------------ the recurrence
+constexpr int RG_CHUNK = 64;
+constexpr int RG_THREADS = 128;
+
+struct RgArgs {
+  const float* gates; int seg, bs;         // [blocks * seg, 2 bs]: row b * seg + t holds r | i of block b
+  const float* a_bias; const float* i_bias; const float* lam; float scale;
+  const float* u;                          // [n, width]
+  const float* proj; long long ld; int y_col; const float* y_bias;
+  int width;
+};
+
+__device__ __forceinline__ float rg_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float rg_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float rg_gelu_tanh(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// the token's decay a and input term sqrt(1 - a^2) * i * u for channel e = (b, c)
+__device__ __forceinline__ void rg_token(const RgArgs& g, int t, int e, int b, int c, float sp, float& a, float& in) {
+  const float* row = g.gates + ((size_t)b * g.seg + t) * (2 * g.bs);
+  const float r = rg_sigmoid(row[c] + g.a_bias[e]);
+  const float i = rg_sigmoid(row[g.bs + c] + g.i_bias[e]);
+  const float loga = -g.scale * r * sp;
+  a = expf(loga);
+  in = sqrtf(fmaxf(-expm1f(2.f * loga), 0.f)) * i * g.u[(size_t)t * g.width + e];
+}
+
+// MODE 0: a thread walks all tokens of (request, channel) from the slot's state and writes it back.
+// MODE 1: a thread forms the map of (chunk, channel) from zero; chunk 0 of a request sets the slot's state aside.
+// MODE 2: a thread folds the earlier chunks' maps onto the state set aside, walks its chunk, writes outputs (and the state
+//         after the request's last chunk).
+// scratch: [requests][width] states set aside, then [chunk slots][2][width] maps; chunk slots are numbered request by
+// request, ceil(len / RG_CHUNK) each.
+template <typename TO, int MODE>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_scan_kernel(RgArgs g, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_q,
+                  const int* __restrict__ seq_lens, TO* __restrict__ out, float* __restrict__ scratch, int requests) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int e = blockIdx.y * RG_THREADS + threadIdx.x;
+  int r, first_chunk = 0, chunk = 0;
+  if (MODE == 0) {
+    r = blockIdx.x;
+  } else {
+    int acc = 0;
+    for (r = 0; r < requests; ++r) {
+      const int cnt = (cu_q[r + 1] - cu_q[r] + RG_CHUNK - 1) / RG_CHUNK;
+      if ((int)blockIdx.x < acc + cnt) break;
+      acc += cnt;
+    }
+    if (r >= requests) return;
+    first_chunk = acc;
+    chunk = blockIdx.x - acc;
+  }
+  if (e >= g.width) return;
+  const int q0 = cu_q[r], len = cu_q[r + 1] - q0;
+  const int lo = MODE == 0 ? 0 : chunk * RG_CHUNK, hi = MODE == 0 ? len : min(len, lo + RG_CHUNK);
+  if (seq_lens[r] <= 0) {                              // a padding row: no state, zeros out
+    if (MODE != 1)
+      for (int t = q0 + lo; t < q0 + hi; ++t) out[(size_t)t * g.width + e] = from_f32<TO>(0.f);
+    return;
+  }
+  const int b = e / g.bs, c = e - b * g.bs;
+  const float sp = rg_softplus(g.lam[e]);
+  float* st = state + (size_t)state_slots[r] * g.width + e;
+  float* aside = scratch + (size_t)r * g.width + e;
+  float* maps = scratch + (size_t)requests * g.width;
+  if (MODE == 1) {
+    if (chunk == 0) *aside = *st;
+    float A = 1.f, B = 0.f;
+    for (int t = q0 + lo; t < q0 + hi; ++t) {
+      float a, in;
+      rg_token(g, t, e, b, c, sp, a, in);
+      A *= a;
+      B = fmaf(a, B, in);
+    }
+    maps[((size_t)(first_chunk + chunk) * 2) * g.width + e] = A;
+    maps[((size_t)(first_chunk + chunk) * 2 + 1) * g.width + e] = B;
+    return;
+  }
+  float S = MODE == 0 ? *st : *aside;
+  if (MODE == 2)
+    for (int k = 0; k < chunk; ++k)
+      S = fmaf(maps[((size_t)(first_chunk + k) * 2) * g.width + e], S, maps[((size_t)(first_chunk + k) * 2 + 1) * g.width + e]);
+  const float yb = g.y_bias[e];
+  for (int t = q0 + lo; t < q0 + hi; ++t) {
+    float a, in;
+    rg_token(g, t, e, b, c, sp, a, in);
+    S = fmaf(a, S, in);
+    out[(size_t)t * g.width + e] = from_f32<TO>(S * rg_gelu_tanh(g.proj[(size_t)t * g.ld + g.y_col + e] + yb));
+  }
+  if (MODE == 0 || hi == len) *st = S;
+}
+
+IFB_EXPORT long long ifb_rglru_scratch_floats(int n, int requests, int width) {
+  const long long chunks = (long long)(n + RG_CHUNK - 1) / RG_CHUNK + requests;
+  return ((long long)requests + 2 * chunks) * width;
+}
+
+template <typename TO>
+static int rg_launch(const RgArgs& g, float* state, const int* state_slots, const int* cu_q, const int* seq_lens, TO* out,
+                     float* scratch, int requests, int n, cudaStream_t stream) {
+  const unsigned ey = (unsigned)((g.width + RG_THREADS - 1) / RG_THREADS);
+  if (scratch == nullptr)
+    return ifb_launch(rglru_scan_kernel<TO, 0>, dim3(requests, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q,
+                      seq_lens, out, scratch, requests);
+  const unsigned chunks = (unsigned)((n + RG_CHUNK - 1) / RG_CHUNK + requests);
+  const int rc = ifb_launch(rglru_scan_kernel<TO, 1>, dim3(chunks, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q,
+                            seq_lens, out, scratch, requests);
+  if (rc != IFB_OK) return rc;
+  return ifb_launch(rglru_scan_kernel<TO, 2>, dim3(chunks, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q, seq_lens,
+                    out, scratch, requests);
+}
+
+// scratch null: the one-launch walk; else the chunked form (ifb_rglru_scratch_floats floats)
+IFB_EXPORT int ifb_rglru_scan(const float* gates, int seg, int blocks, const float* a_bias, const float* i_bias, const float* lam,
+                              float scale, const float* u, const float* proj, long long ld, int y_col, const float* y_bias,
+                              float* state, const int* state_slots, const int* cu_q, const int* seq_lens, void* out, int out_dtype,
+                              float* scratch, int requests, int n, int width, cudaStream_t stream) {
+  if (n <= 0 || requests <= 0) return IFB_OK;
+  if (width < 1 || blocks < 1 || width % blocks || seg < n || y_col < 0 || y_col + width > ld) return IFB_ERR_SIZE;
+  const RgArgs g{gates, seg, width / blocks, a_bias, i_bias, lam, scale, u, proj, ld, y_col, y_bias, width};
+  if (out_dtype == IFB_BF16)
+    return rg_launch<__nv_bfloat16>(g, state, state_slots, cu_q, seq_lens, (__nv_bfloat16*)out, scratch, requests, n, stream);
+  if (out_dtype != IFB_F32) return IFB_ERR_DTYPE;
+  return rg_launch<float>(g, state, state_slots, cu_q, seq_lens, (float*)out, scratch, requests, n, stream);
+}

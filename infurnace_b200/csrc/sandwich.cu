@@ -120,19 +120,29 @@ IFB_EXPORT int ifb_add_rows(float* x, const float* rows, const void* vec, int ve
   return ifb_launch(add_rows_kernel, dim3(blocks), dim3(256), 0, stream, x, rows, vec, vec_dtype, accumulate, total, hidden);
 }
 
-// total[i] = (accumulate ? total[i] : 0) + scale * d[i]
+// total[i] = (accumulate ? total[i] : 0) + scale * d[i]; copy[i] (optional, bfloat16 or float32) = the new total[i], for
+// the product that reads the stream next
 __global__ void __launch_bounds__(256)
-scaled_sum_kernel(float* __restrict__ total, const float* __restrict__ d, float scale, int accumulate, long long count) {
+scaled_sum_kernel(float* __restrict__ total, const float* __restrict__ d, float scale, int accumulate, long long count,
+                  void* __restrict__ copy, int copy_dtype) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
-    total[i] = accumulate ? fmaf(scale, d[i], total[i]) : scale * d[i];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const float v = accumulate ? fmaf(scale, d[i], total[i]) : scale * d[i];
+    total[i] = v;
+    if (copy != nullptr) {
+      if (copy_dtype == IFB_BF16) reinterpret_cast<__nv_bfloat16*>(copy)[i] = __float2bfloat16(v);
+      else reinterpret_cast<float*>(copy)[i] = v;
+    }
+  }
 }
 
-IFB_EXPORT int ifb_scaled_sum(float* total, const float* d, float scale, int accumulate, long long count, cudaStream_t stream) {
+IFB_EXPORT int ifb_scaled_sum(float* total, const float* d, float scale, int accumulate, long long count, void* copy,
+                              int copy_dtype, cudaStream_t stream) {
   if (count <= 0) return IFB_OK;
+  if (copy != nullptr && copy_dtype != IFB_BF16 && copy_dtype != IFB_F32) return IFB_ERR_DTYPE;
   const unsigned blocks = (unsigned)min((count + 255) / 256, (long long)65535);
-  return ifb_launch(scaled_sum_kernel, dim3(blocks), dim3(256), 0, stream, total, d, scale, accumulate, count);
+  return ifb_launch(scaled_sum_kernel, dim3(blocks), dim3(256), 0, stream, total, d, scale, accumulate, count, copy, copy_dtype);
 }
 
 // ------------------------------------------------------------------------------------------

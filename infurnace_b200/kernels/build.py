@@ -38,8 +38,8 @@ LIBRARIES: Dict[str, tuple] = {
     # post-norm sublayers (embedding with a position vector, residual update), the gated recurrence, talking attention
     "mixers": (["sublayer.cu", "gated_scan.cu", "attention_talk.cu", "attention_talk_mma.cu"], []),
     # sandwich-norm blocks, recurrences over a matrix state or an element-wise one, attention with rotated values over
-    # page streams, routed experts
-    "hybrid": (["sandwich.cu", "linear_scan.cu", "attention_streams.cu", "moe.cu"], []),
+    # page streams, routed experts, the real-gated linear recurrent unit with its convolution
+    "hybrid": (["sandwich.cu", "linear_scan.cu", "attention_streams.cu", "moe.cu", "rglru.cu"], []),
     # decoders with latent attention: norms in groups, the short causal convolution, the average over depth, the
     # preparation of queries and latents, attention over cached latents (plain and on tensor cores), the output gate
     "latent": (["latent.cu", "attention_latent.cu", "attention_latent_mma.cu"], []),

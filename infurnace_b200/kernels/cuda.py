@@ -78,7 +78,7 @@ class CudaKernels:
         c.ifb_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                              c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                              c_void_p]
-        c.ifb_rope_table.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        c.ifb_rope_table.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p]
         c.ifb_sample.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         c.ifb_argmax_rows.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         self._argmax_scratch = None    # (values, indices, counters) of the several-blocks-per-row argmax
@@ -116,6 +116,8 @@ class CudaKernels:
         self._ls_scratch = None
         self._gu_scratch = None
         self.gated_unit_chunked_calls = 0
+        self._rg_scratch = None
+        self.rglru_chunked_calls = 0
         self.moe_tensor_cores = os.environ.get("INFURNACE_MOE_MMA", "1") != "0"
         self.moe_tcgen05 = os.environ.get("INFURNACE_MOE_TCGEN05", "1") != "0"     # prompts' expert products on tcgen05
         self.moe_tcgen05_calls = 0
@@ -500,15 +502,15 @@ class CudaKernels:
             "linear_qkv_rope_store")
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
-    def rope_table(self, positions, inv_freq, out):
-        """out[tok, i] = (cos, sin)(positions[tok] * inv_freq[i]), float32 ``[tokens, 2 * len(inv_freq)]``."""
+    def rope_table(self, positions, inv_freq, out, gain=1.0):
+        """out[tok, i] = gain * (cos, sin)(positions[tok] * inv_freq[i]), float32 ``[tokens, 2 * len(inv_freq)]``."""
         _dense(positions, "positions", torch.int32), _dense(inv_freq, "inv_freq", torch.float32)
         _dense(out, "out", torch.float32)
         n, half = positions.numel(), inv_freq.numel()
         if out.shape != (n, 2 * half):
             raise KernelError("rope_table: out is [tokens, 2 * len(inv_freq)]")
         self.launches += 1
-        _check(self.core.ifb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), half, out.data_ptr(), n, self._stream()),
+        _check(self.core.ifb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), half, out.data_ptr(), n, float(gain), self._stream()),
                "rope_table")
 
     def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, inv_freq,
@@ -858,7 +860,7 @@ class CudaKernels:
             m.ifb_residual_norm_update.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_void_p, c_int,
                                                    c_float, c_void_p, c_int, c_int, c_int, c_void_p]
             m.ifb_add_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
-            m.ifb_scaled_sum.argtypes = [c_void_p, c_void_p, c_float, c_int, c_longlong, c_void_p]
+            m.ifb_scaled_sum.argtypes = [c_void_p, c_void_p, c_float, c_int, c_longlong, c_void_p, c_int, c_void_p]
             m.ifb_token_side_gate.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
                                               c_int, c_int, c_void_p]
             m.ifb_softcap.argtypes = [c_void_p, c_float, c_longlong, c_void_p]
@@ -877,7 +879,7 @@ class CudaKernels:
             m.ifb_gated_unit_scratch_floats.argtypes = [c_int, c_int, c_int]
             m.ifb_rotary_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
                                            c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
-                                           c_int, c_int, c_void_p]
+                                           c_int, c_int, c_int, c_void_p]
             m.ifb_rotate_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_paged_attention_streams.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
                                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -891,6 +893,16 @@ class CudaKernels:
                                                    c_int, c_int, c_int, c_int, c_float, c_void_p]
             m.ifb_moe_plan_padded.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
             m.ifb_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+            m.ifb_rglru_conv.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_void_p]
+            m.ifb_rglru_scratch_floats.restype = c_longlong
+            m.ifb_rglru_scratch_floats.argtypes = [c_int, c_int, c_int]
+            m.ifb_rglru_scan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                         c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_gather_scaled.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                c_void_p]
         return self._hyb
 
     def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None, y2=None, scale=1.0, scale2=1.0):
@@ -925,14 +937,14 @@ class CudaKernels:
         _check(self._hyb_lib().ifb_add_rows(x.data_ptr(), _ptr(rows), _ptr(vec), _code(vec) if vec is not None else 0,
                                             1 if accumulate else 0, n, hidden, self._stream()), "add_rows")
 
-    def scaled_sum(self, total, d, scale, accumulate=True):
-        """total (+)= scale * d (float32, same shape)."""
+    def scaled_sum(self, total, d, scale, accumulate=True, copy=None):
+        """total (+)= scale * d (float32, same shape); ``copy`` (bfloat16 or float32, same shape) also gets the new total."""
         _dense(total, "total", torch.float32), _dense(d, "d", torch.float32)
-        if total.shape != d.shape:
-            raise KernelError("scaled_sum: total and d differ in shape")
+        if total.shape != d.shape or (copy is not None and _dense(copy, "copy").shape != total.shape):
+            raise KernelError("scaled_sum: total, d and copy differ in shape")
         self.launches += 1
         _check(self._hyb_lib().ifb_scaled_sum(total.data_ptr(), d.data_ptr(), float(scale), 1 if accumulate else 0, d.numel(),
-                                              self._stream()), "scaled_sum")
+                                              _ptr(copy), _code(copy) if copy is not None else 0, self._stream()), "scaled_sum")
 
     def token_side_gate(self, z, table, ids, offset, activation, out):
         """out[n, j] = act(z[n, j]) * table[ids[n], offset + j]."""
@@ -1053,6 +1065,65 @@ class CudaKernels:
                                                    out.data_ptr(), _code(out), r, n, width, scratch, self._stream()),
                "gated_unit_scan")
 
+    def rglru_conv(self, proj, x_col, x_bias, conv_weight, conv_bias, state, state_slots, cu_q, seq_lens, req_index, u, u_blocks,
+                   offsets, tile_block=None, tile=0):
+        """The short causal convolution in front of a real-gated recurrence (csrc/rglru.cu): per channel
+        u_t = conv_bias + sum_j conv_weight[:, j] * xin_(t - taps + 1 + j), xin = proj[:, x_col : x_col + width] + x_bias, over
+        each request's tokens; the taps - 1 inputs before a portion come from state[slot] ([slots, max(taps - 1, 1), width]
+        float32), which then takes the portion's last inputs.  u [n, width] float32; u_blocks [blocks, seg, width / blocks]
+        in the products' dtype holds the same numbers block-major for the grouped gate products, whose segments go to
+        offsets [blocks + 1] (and tile_block [blocks * seg / tile]).  The parameters are float32."""
+        _dense(proj, "proj", torch.float32), _dense(u, "u", torch.float32), _dense(u_blocks, "u_blocks"), _dense(state, "state", torch.float32)
+        for t, name in ((x_bias, "x_bias"), (conv_weight, "conv_weight"), (conv_bias, "conv_bias")):
+            _dense(t, name, torch.float32)
+        _dense(offsets, "offsets", torch.int32)
+        n, width = u.shape
+        blocks, seg, bs = u_blocks.shape
+        taps = conv_weight.shape[1]
+        if blocks * bs != width or seg < n or proj.shape[0] != n or conv_weight.shape[0] != width or x_bias.numel() != width \
+                or conv_bias.numel() != width or state.shape[1:] != (max(taps - 1, 1), width) or offsets.numel() != blocks + 1:
+            raise KernelError("rglru_conv: sizes of proj, parameters, state, u and u_blocks do not match")
+        if tile_block is not None and _dense(tile_block, "tile_block", torch.int32).numel() * tile != blocks * seg:
+            raise KernelError("rglru_conv: tile_block has an entry for every tile of rows")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_rglru_conv(
+            proj.data_ptr(), proj.shape[1], int(x_col), x_bias.data_ptr(), conv_weight.data_ptr(), conv_bias.data_ptr(),
+            state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), req_index.data_ptr(), u.data_ptr(),
+            u_blocks.data_ptr(), _code(u_blocks), seg, blocks, offsets.data_ptr(), _ptr(tile_block), int(tile), n, width, taps,
+            self._stream()), "rglru_conv")
+
+    def rglru_scan(self, gates, a_bias, i_bias, decay, decay_scale, u, proj, y_col, y_bias, state, state_slots, cu_q, seq_lens, out,
+                   max_q_len=1):
+        """The real-gated linear recurrence over this step's tokens of every request (csrc/rglru.cu).  gates
+        [blocks, seg, 2 bs] float32: the block-diagonal products' raw r | i; r = sigmoid(. + a_bias), i = sigmoid(. + i_bias),
+        log a = -decay_scale * r * softplus(decay), S <- a S + sqrt(1 - a^2) * i * u on state [slots, width] float32;
+        out = S * gelu_tanh(proj[:, y_col : y_col + width] + y_bias).  From ``scan_block_min`` tokens on the requests are
+        cut into chunks of 64 tokens that run side by side (two launches), which differs by rounding only."""
+        _dense(gates, "gates", torch.float32), _dense(u, "u", torch.float32), _dense(proj, "proj", torch.float32)
+        _dense(state, "state", torch.float32), _dense(out, "out")
+        for t, name in ((a_bias, "a_bias"), (i_bias, "i_bias"), (decay, "decay"), (y_bias, "y_bias")):
+            _dense(t, name, torch.float32)
+        n, width = out.shape
+        blocks, seg, two_bs = gates.shape
+        r = seq_lens.numel()
+        if blocks * two_bs != 2 * width or seg < n or u.shape != (n, width) or proj.shape[0] != n or state.shape[1:] != (width,) \
+                or any(t.numel() != width for t in (a_bias, i_bias, decay, y_bias)) or cu_q.numel() != r + 1 or state_slots.numel() < r:
+            raise KernelError("rglru_scan: sizes of gates, parameters, u, proj, state and out do not match")
+        lib = self._hyb_lib()
+        scratch = 0
+        if max_q_len >= self.scan_block_min:
+            need = int(lib.ifb_rglru_scratch_floats(n, r, width))
+            if self._rg_scratch is None or self._rg_scratch.numel() < need:
+                self._rg_scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+                self.scratch_generation += 1
+            scratch = self._rg_scratch.data_ptr()
+            self.rglru_chunked_calls += 1
+        self.launches += 2 if scratch else 1
+        _check(lib.ifb_rglru_scan(gates.data_ptr(), seg, blocks, a_bias.data_ptr(), i_bias.data_ptr(), decay.data_ptr(),
+                                  float(decay_scale), u.data_ptr(), proj.data_ptr(), proj.shape[1], int(y_col), y_bias.data_ptr(),
+                                  state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+                                  _code(out), scratch, r, n, width, self._stream()), "rglru_scan")
+
     @staticmethod
     def _stream_pages(t, name, heads, width, dtype):
         """(address, elements between pages, page size) of a page stream [pages, heads, page_size, width]."""
@@ -1062,13 +1133,14 @@ class CudaKernels:
         return t.data_ptr(), t.stride(0), t.shape[2]
 
     def rotary_store(self, qkv, num_heads, num_kv_heads, head_dim, value_head_dim, qk_table, rotary_dim, interleaved, value_eps,
-                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping):
+                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping, values_are_keys=False):
         """Rotation of q and k, norm and rotation of v, q row and page stores in one launch (csrc/attention_streams.cu).
-        qkv float32 [n, H d + G d + G dv]; tables float32 (cos, sin) pairs per token; value_eps None: no value norm."""
+        qkv float32 [n, H d + G d + G dv]; tables float32 (cos, sin) pairs per token; value_eps None: no value norm.
+        ``values_are_keys``: qkv is [n, H d + G d] and a value head is its key head before the rotation."""
         _dense(qkv, "qkv", torch.float32), _dense(q_out, "q_out")
         n = qkv.shape[0]
         H, G, d, dv = num_heads, num_kv_heads, head_dim, value_head_dim
-        if qkv.shape[1] != H * d + G * (d + dv) or q_out.shape != (n, H * d):
+        if qkv.shape[1] != H * d + G * (d + (0 if values_are_keys else dv)) or q_out.shape != (n, H * d) or (values_are_keys and dv != d):
             raise KernelError("rotary_store: widths of qkv and q_out do not match the heads")
         if qk_table is not None and _dense(qk_table, "qk_table", torch.float32).shape != (n, rotary_dim):
             raise KernelError("rotary_store: qk_table is [tokens, rotary_dim]")
@@ -1085,7 +1157,8 @@ class CudaKernels:
         _check(self._hyb_lib().ifb_rotary_store(
             qkv.data_ptr(), qkv.shape[1], H, G, d, dv, _ptr(qk_table), int(rotary_dim), int(bool(interleaved)),
             0 if value_eps is None else 1, float(value_eps or 0.0), _ptr(v_table), int(bool(v_interleaved)), q_out.data_ptr(),
-            _code(q_out), pk[0], pk[1], pv[0], pv[1], _ptr(slot_mapping), ps, n, self._stream()), "rotary_store")
+            _code(q_out), pk[0], pk[1], pv[0], pv[1], _ptr(slot_mapping), ps, n, 1 if values_are_keys else 0, self._stream()),
+            "rotary_store")
 
     def rotate_rows(self, rows, table, heads, width, dims, interleaved, back=False):
         """rows [n, heads * width] in place: every head's first ``dims`` entries turned by the token's angles of
@@ -1126,19 +1199,20 @@ class CudaKernels:
     def _route_mode(logits, experts, scoring, groups, weight_scale):
         """(experts, stride, mode, group count, groups kept, weight scale) of a router call: ``experts`` None means every
         column of ``logits`` is an expert's."""
-        if scoring not in ("chosen", "all"):
-            raise KernelError(f"moe_route: scoring {scoring!r}; known: chosen, all")
+        if scoring not in ("chosen", "all", "sigmoid"):
+            raise KernelError(f"moe_route: scoring {scoring!r}; known: chosen, all, sigmoid")
         count, keep = groups if groups else (1, 1)
         if groups and scoring != "all":
             raise KernelError("moe_route: groups of experts limit the choice only with scoring 'all'")
-        return (int(experts) if experts is not None else logits.shape[1], logits.shape[1], 1 if scoring == "all" else 0,
+        return (int(experts) if experts is not None else logits.shape[1], logits.shape[1], {"chosen": 0, "all": 1, "sigmoid": 2}[scoring],
                 int(count), int(keep), float(weight_scale))
 
     def moe_route(self, logits, top, ids, gates, experts=None, scoring="chosen", groups=None, weight_scale=1.0):
         """ids[n] = the indices of row n's ``top`` largest scores, largest first (the lower index among equals).  scoring
         "chosen": the scores are the logits and gates[n] = the softmax over the chosen logits.  scoring "all": the scores are
         the softmax over all experts, gates[n] = score * weight_scale, and with ``groups`` = (count, keep) only experts of the
-        ``keep`` groups of neighbours with the largest best score can be chosen.  ``experts``: the first that many columns of
+        ``keep`` groups of neighbours with the largest best score can be chosen.  scoring "sigmoid": the scores are sigmoid(logit)
+        per expert and gates[n] = score * weight_scale.  ``experts``: the first that many columns of
         ``logits`` are the router's (the rest belong to someone else).  (csrc/moe.cu)"""
         _dense(logits, "logits", torch.float32), _dense(ids, "ids", torch.int32), _dense(gates, "gates", torch.float32)
         n = logits.shape[0]
@@ -1243,6 +1317,20 @@ class CudaKernels:
         _check(self._hyb_lib().ifb_moe_gather_rows(x.data_ptr(), perm.data_ptr(), int(top), tile_expert.data_ptr(), self.MOE_TILE,
                                                    out.data_ptr(), perm.numel(), x.shape[1], self._stream()), "moe_gather")
 
+    def moe_gather_scaled(self, x, perm, top, gates, out, tile_expert=None):
+        """out[place] = gates[perm[place]] * x[perm[place] // top] in out's dtype, zeros where perm[place] < 0: what the experts
+        read when their weight multiplies their input.  ``gates`` float32 [rows, top] (pair = row * top + choice);
+        ``tile_expert``: the padded list's tiles, whose unused ones are left alone."""
+        _dense(x, "x"), _dense(perm, "perm", torch.int32), _dense(gates, "gates", torch.float32), _dense(out, "out", x.dtype)
+        if out.shape != (perm.numel(), x.shape[1]) or gates.numel() != x.shape[0] * top:
+            raise KernelError("moe_gather_scaled: out has a row for every place of perm, gates a number for every pair")
+        if tile_expert is not None and _dense(tile_expert, "tile_expert", torch.int32).numel() * self.MOE_TILE != perm.numel():
+            raise KernelError("moe_gather_scaled: tile_expert has an entry for every tile of places")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_gather_scaled(x.data_ptr(), _code(x), perm.data_ptr(), int(top), gates.data_ptr(),
+                                                     _ptr(tile_expert), self.MOE_TILE, out.data_ptr(), perm.numel(), x.shape[1],
+                                                     self._stream()), "moe_gather_scaled")
+
     def moe_linear_grouped(self, x, w, tile_expert, out, epilogue="none"):
         """out[place] = x[place] @ w[tile_expert[place // tile]]^T on the tcgen05 kernel (csrc/linear_tcgen05.cu, its grouped
         mode); x [places, k] sorted by expert in padded segments, w [experts, o (2 o with "silu_gate"), k]."""
@@ -1270,9 +1358,14 @@ class CudaKernels:
         """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32 (y may hold more rows than pairs: a
         padded list).  ``shared`` [n, width] float32: + shared[n], times sigmoid(shared_logit[n]) when ``shared_logit`` (a
         column of a float32 matrix) is given."""
-        _dense(y, "y", torch.float32), _dense(pos, "pos", torch.int32), _dense(gates, "gates", torch.float32)
-        _dense(out, "out", torch.float32)
-        n, top = gates.shape
+        _dense(y, "y", torch.float32), _dense(pos, "pos", torch.int32), _dense(out, "out", torch.float32)
+        n = out.shape[0]
+        if gates is None:                      # every weight is 1 (the weights went into what the experts read)
+            top = pos.numel() // max(n, 1)
+        else:
+            top = _dense(gates, "gates", torch.float32).shape[1]
+            if gates.shape[0] != n:
+                raise KernelError("moe_combine: gates has a row for every row of out")
         if pos.numel() != n * top or y.shape[0] < n * top or y.shape[1] != out.shape[1] or out.shape[0] != n:
             raise KernelError("moe_combine: sizes of y, pos, gates and out do not match")
         stride = 0
@@ -1284,7 +1377,7 @@ class CudaKernels:
                     raise KernelError("moe_combine: shared_logit is one float32 number per row")
                 stride = shared_logit.stride(0)
         self.launches += 1
-        _check(self._hyb_lib().ifb_moe_combine(y.data_ptr(), pos.data_ptr(), gates.data_ptr(), out.data_ptr(), n, top,
+        _check(self._hyb_lib().ifb_moe_combine(y.data_ptr(), pos.data_ptr(), _ptr(gates), out.data_ptr(), n, top,
                                                out.shape[1], _ptr(shared), _ptr(shared_logit) if shared is not None else None,
                                                stride, self._stream()), "moe_combine")
 
@@ -1300,8 +1393,8 @@ class CudaKernels:
                                           c_void_p, c_int, c_int, c_int, c_void_p]
             m.ifb_latent_prepare.argtypes = [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float,
                                              c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                             c_void_p, c_void_p, c_int, c_int, c_void_p]
-            m.ifb_gate_heads.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+                                             c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p]
+            m.ifb_gate_heads.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_latent_attention.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                c_float, c_int, c_void_p]
@@ -1367,18 +1460,22 @@ class CudaKernels:
                                                out.data_ptr(), n, width, taps, self._stream()), "causal_conv")
 
     def latent_prepare(self, proj, heads, dim, rot, rank, down_col, norm_weight, eps, table, dims, q_plain, q_rot, latent_pages,
-                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0):
+                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0, q=None, interleaved=False):
         """From a step's product q | latent, rotated key | ... (proj, float32): the normalised latent and the turned rotated
         key part into their page streams ([pages, 1, page_size, width]) at slot_mapping (None: nothing is stored), the
         heads' unrotated query parts head-major into q_plain [heads, seg, dim], their turned rotated parts into q_rot
         [n, heads, rot] (float32).  offsets [heads + 1] gets the segments h * seg of the grouped products that follow,
-        tile_head [heads * seg / tile] the head of every tile of rows.  table [n, dims]: (cos, sin) pairs (None: no turn)."""
+        tile_head [heads * seg / tile] the head of every tile of rows.  table [n, dims]: (cos, sin) pairs (None: no turn);
+        ``interleaved``: a rotation pairs entry 2m with 2m + 1 instead of m with m + dims/2.  ``q`` [n, heads * (dim + rot)]
+        float32: the queries come from there (a product of their own) and ``proj`` need not hold them."""
         _dense(proj, "proj", torch.float32), _dense(q_plain, "q_plain"), _dense(latent_pages, "latent_pages", q_plain.dtype)
         _dense(offsets, "offsets", torch.int32), _dense(norm_weight, "norm_weight")
         n, stride = proj.shape
         seg = q_plain.shape[1]
+        if q is not None and _dense(q, "q", torch.float32).shape != (n, heads * (dim + rot)):
+            raise KernelError("latent_prepare: q is float32 [n, heads * (dim + rot)]")
         if q_plain.shape != (heads, seg, dim) or seg < n or offsets.numel() != heads + 1 or norm_weight.numel() != rank \
-                or latent_pages.shape[1] != 1 or latent_pages.shape[3] != rank or heads * (dim + rot) > down_col \
+                or latent_pages.shape[1] != 1 or latent_pages.shape[3] != rank or (q is None and heads * (dim + rot) > down_col) \
                 or down_col + rank + rot > stride:
             raise KernelError("latent_prepare: sizes of proj, q_plain, latent_pages and offsets do not match")
         if rot:
@@ -1395,6 +1492,7 @@ class CudaKernels:
                                                   q_plain.data_ptr(), _code(q_plain), seg, _ptr(q_rot) if rot else None,
                                                   latent_pages.data_ptr(), _ptr(rot_pages) if rot else None, _code(latent_pages),
                                                   _ptr(slot_mapping), offsets.data_ptr(), _ptr(tile_head), int(tile), n,
+                                                  _ptr(q), q.shape[1] if q is not None else 0, 1 if interleaved else 0,
                                                   self._stream()), "latent_prepare")
 
     def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
@@ -1445,21 +1543,22 @@ class CudaKernels:
                                                     out.data_ptr(), _code(out), int(tokens), heads, rank, rot, float(scale),
                                                     int(window or 0), self._stream()), "latent_attention")
 
-    def gate_heads(self, y, gate, out, tokens):
+    def gate_heads(self, y, gate, out, tokens, per_head=False):
         """out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (gate None: no gate); y [heads, seg, vdim]
-        float32, gate a float32 view [n, heads * vdim] whose rows may be strided."""
+        float32, gate a float32 view [n, heads * vdim] whose rows may be strided.  ``per_head``: gate is [n, heads] and a
+        head takes one number."""
         _dense(y, "y", torch.float32), _dense(out, "out")
         heads, seg, vdim = y.shape
         if out.shape != (tokens, heads * vdim) or seg < tokens:
             raise KernelError("gate_heads: out is [tokens, heads * vdim]")
         stride = 0
         if gate is not None:
-            if gate.dtype != torch.float32 or gate.shape != out.shape or gate.stride(1) != 1:
+            if gate.dtype != torch.float32 or gate.shape != ((tokens, heads) if per_head else out.shape) or gate.stride(1) != 1:
                 raise KernelError("gate_heads: gate is a float32 view of out's shape with unit stride along the row")
             stride = gate.stride(0)
         self.launches += 1
         _check(self._lat_lib().ifb_gate_heads(y.data_ptr(), seg, _ptr(gate), stride, out.data_ptr(), _code(out), int(tokens), heads,
-                                              vdim, self._stream()), "gate_heads")
+                                              vdim, 1 if per_head else 0, self._stream()), "gate_heads")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

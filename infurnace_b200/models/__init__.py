@@ -8,3 +8,4 @@ from . import qwen3  # noqa: F401  (registers "Qwen3ForCausalLM")
 from . import kafunex  # noqa: F401  (registers "Kafunex")
 from . import lunelorn  # noqa: F401  (registers "Lunelorn")
 from . import filorax  # noqa: F401  (registers "Filorax")
+from . import golonex  # noqa: F401  (registers "Golonex")

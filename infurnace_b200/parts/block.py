@@ -14,19 +14,28 @@ class PreNormBlock:
     """x += mixer(norm(x)); x += ffn(norm(x))
     (src/infurnace/executor/tinygrad/model.py:101,143,145,148).  Each addition happens in
     the kernel of the norm that follows it, so the block takes the previous block's last
-    delta as ``pending`` and hands its own on."""
+    delta as ``pending`` and hands its own on.
+
+    A block without feed-forward hands on the mixer's delta.  A block with a per-layer token input
+    (``side``) ends with the stream up to date: the last delta is added in a pass that also leaves
+    the stream in the products' dtype for the side input's gate product, the side input's result is
+    normalised and added by the framework's stream update kernel, which in the same pass writes the
+    NEXT block's first norm when a block of this kind follows (it gets a :class:`ReadyInput`)."""
 
     def __init__(self, spec: PreNormBlockSpec, weights, runtime):
         self.spec = spec
         self.rt = runtime
+        self.k = runtime.kernels
         self.mixer_norm = build_part(spec.mixer_norm, weights, runtime)
         self.mixer = build_part(spec.mixer, weights, runtime)
-        self.ffn_norm = build_part(spec.ffn_norm, weights, runtime)
-        self.ffn = build_part(spec.ffn, weights, runtime)
+        self.ffn_norm = build_part(spec.ffn_norm, weights, runtime) if spec.ffn is not None else None
+        self.ffn = build_part(spec.ffn, weights, runtime) if spec.ffn is not None else None
+        self.side = build_part(spec.side, weights, runtime) if spec.side is not None else None
 
     @property
     def graph_safe(self):
-        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn))
+        parts = [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.side) if p is not None]
+        return all(getattr(p, "graph_safe", False) for p in parts)
 
     folds_norms = True
 
@@ -38,11 +47,16 @@ class PreNormBlock:
 
     def forward(self, x, pending, ctx, call, next_layer=None):
         n = x.shape[0]
-        if isinstance(pending, Folded):              # x is up to date and our first norm is folded
+        if isinstance(pending, ReadyInput):          # x is up to date and our first norm is written
+            h = pending.values
+        elif isinstance(pending, Folded):            # x is up to date and our first norm is folded
             h = pending
         else:
             h = ctx.buffer("h", x.shape, self.rt.act_dtype)
             self.mixer_norm.forward(x, h, delta=pending)
+        if self.ffn is None:
+            d = self.mixer.forward(h, ctx, call)
+            return self._finish(x, d, ctx, next_layer)
         take = getattr(self.ffn, "can_take_folded", None)
         if getattr(self.mixer, "can_fold_output", False) and getattr(self.ffn_norm, "foldable", False) and take and take(n):
             d = self.mixer.forward(h, ctx, call, fold=(x, self.ffn_norm))
@@ -53,9 +67,33 @@ class PreNormBlock:
         else:
             h = ctx.buffer("h", x.shape, self.rt.act_dtype)
             self.ffn_norm.forward(x, h, delta=d)
-        if next_layer is not None and getattr(self.ffn, "can_fold_output", False) and next_layer.takes_folded(n):
+        if self.side is None and next_layer is not None and getattr(self.ffn, "can_fold_output", False) and next_layer.takes_folded(n):
             return self.ffn.forward(h, ctx, fold=(x, next_layer.mixer_norm))
-        return self.ffn.forward(h, ctx)
+        return self._finish(x, self.ffn.forward(h, ctx), ctx, next_layer)
+
+    def _finish(self, x, d, ctx, next_layer):
+        """The block's last delta: handed on as it is, or, with a side input, added here before that input reads the stream."""
+        if self.side is None:
+            return d
+        k = self.k
+        if self.rt.act_dtype == torch.float32:
+            k.scaled_sum(x, d, 1.0)
+            xa = x
+        else:
+            xa = ctx.buffer("stream_copy", x.shape, self.rt.act_dtype)
+            k.scaled_sum(x, d, 1.0, copy=xa)
+        y = self.side.forward(xa, ctx)
+        ahead = None
+        if isinstance(next_layer, PreNormBlock) and hasattr(next_layer.mixer_norm, "weight") \
+                and type(next_layer.mixer_norm) is type(self.side.norm):
+            ahead = next_layer.mixer_norm
+        norm = self.side.norm
+        if ahead is not None and ahead.spec.eps == norm.spec.eps:
+            out = ctx.buffer("h", x.shape, self.rt.act_dtype)
+            k.residual_norm_update(x, y, norm.weight, norm.spec.eps, out=out, next_weight=ahead.weight)
+            return ReadyInput(out)
+        k.residual_norm_update(x, y, norm.weight, norm.spec.eps)
+        return None
 
 
 register_part(PreNormBlockSpec, PreNormBlock)

@@ -20,7 +20,9 @@ class RoutedExperts:
     padded to that kernel's tile of 128 rows (``_forward_padded``); fewer pairs, float32 and odd sizes the kernels of
     csrc/moe.cu.
 
-    The description's ``scoring``, ``groups`` and ``weight_scale`` go to the router kernel as they are.  A ``shared``
+    The description's ``scoring``, ``groups`` and ``weight_scale`` go to the router kernel as they are.  With ``weight_on``
+    "input" an expert reads weight * h: the tokens' rows are gathered into the list's order times their weights (one
+    kernel, which the padded route runs anyway), and the combining kernel adds the results as they are.  A ``shared``
     expert is two dense products on every row; its result joins the weighted sum in the combining kernel, times
     sigmoid of the row's ``shared_gate`` logit when there is one.  That logit is one more row of the router's matrix, so
     it costs no product of its own."""
@@ -45,6 +47,9 @@ class RoutedExperts:
         elif spec.shared_gate is not None:
             raise ModelConfigError("a gate of the shared expert needs a shared expert")
         self.route_args = dict(scoring=spec.scoring, groups=spec.groups, weight_scale=spec.weight_scale)
+        if spec.weight_on not in ("output", "input"):
+            raise ModelConfigError(f"weight_on {spec.weight_on!r}: an expert's weight multiplies its 'output' or its 'input'")
+        self.weight_input = spec.weight_on == "input"
         self.w_gate_up = torch.stack([torch.cat((weights[g], weights[u]), dim=0) for g, u, _ in spec.experts], dim=0).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in spec.experts], dim=0).contiguous()
         self.num_experts = len(spec.experts)
@@ -67,11 +72,16 @@ class RoutedExperts:
         pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
         k.moe_route_plan(logits, s.top, ids, gates, offsets, perm, pos, experts=E, **self.route_args)   # one launch for few pairs
         act = ctx.buffer("moe_act", (pairs, s.intermediate_size), self.rt.act_dtype, rows=ctx.max_rows * s.top)
-        k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
+        if self.weight_input:        # the experts read weight * h: the rows are gathered and scaled into the list's order first
+            xs = ctx.buffer("moe_xs_scaled", (pairs, h.shape[1]), h.dtype, rows=ctx.max_rows * s.top)
+            k.moe_gather_scaled(h, perm, s.top, gates, xs)
+            k.moe_linear(xs, self.w_gate_up, offsets, None, 1, act, epilogue="silu_gate")
+        else:
+            k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
         y = ctx.buffer("moe_y", (pairs, s.hidden_size), torch.float32, rows=ctx.max_rows * s.top)
         k.moe_linear(act, self.w_down, offsets, None, 1, y)
         delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
-        k.moe_combine(y, pos, gates, delta, *shared)
+        k.moe_combine(y, pos, None if self.weight_input else gates, delta, *shared)
         return delta
 
     def _shared(self, h, ctx, logits):
@@ -100,13 +110,16 @@ class RoutedExperts:
         tiles = ctx.buffer("moe_tiles", (places // k.MOE_TILE,), torch.int32, rows=cap // k.MOE_TILE)
         k.moe_plan_padded(ids, E, offsets, perm, pos, tiles)
         xs = ctx.buffer("moe_xs", (places, h.shape[1]), self.rt.act_dtype, rows=cap)
-        k.moe_gather(h, perm, s.top, tiles, xs)
+        if self.weight_input:
+            k.moe_gather_scaled(h, perm, s.top, gates, xs, tile_expert=tiles)
+        else:
+            k.moe_gather(h, perm, s.top, tiles, xs)
         act = ctx.buffer("moe_act_padded", (places, s.intermediate_size), self.rt.act_dtype, rows=cap)
         k.moe_linear_grouped(xs, self.w_gate_up, tiles, act, epilogue="silu_gate")
         y = ctx.buffer("moe_y_padded", (places, s.hidden_size), torch.float32, rows=cap)
         k.moe_linear_grouped(act, self.w_down, tiles, y)
         delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
-        k.moe_combine(y, pos, gates, delta, *shared)
+        k.moe_combine(y, pos, None if self.weight_input else gates, delta, *shared)
         return delta
 
 

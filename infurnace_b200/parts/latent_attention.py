@@ -20,7 +20,8 @@ class LatentAttention:
     streams and lays the heads' unrotated query parts out head-major; a grouped product over the heads with UK_h^T
     (the framework's grouped product, a head being what an expert is there); the attention kernel over the pages, this
     step's tokens included, with window and sink; a grouped product with UV_h; one kernel that applies the output gate
-    and puts the heads side by side; the output product."""
+    and puts the heads side by side; the output product.  Where the queries have a latent of their own, they are two more
+    products with an RMS norm between them, and the first product holds latent, rotated key | gate only."""
 
     graph_safe = True
 
@@ -28,13 +29,19 @@ class LatentAttention:
         self.spec = s = spec
         self.rt = runtime
         self.k = runtime.kernels
-        parts = [weights[s.q_proj], weights[s.down_proj]]
+        H, D, V, R = s.num_heads, s.head_dim, s.value_head_dim, s.kv_rank
+        # with a latent of their own the queries are two products with a norm between them, and the step's first product
+        # holds latent, rotated key | gate only
+        self.q_latent = bool(s.q_rank)
+        parts = [weights[s.down_proj]] if self.q_latent else [weights[s.q_proj], weights[s.down_proj]]
         if s.gate is not None:
             parts.append(weights[s.gate])
         self.w_in = torch.cat(parts, dim=0).contiguous()
-        H, D, V, R = s.num_heads, s.head_dim, s.value_head_dim, s.kv_rank
-        self.down_col = H * (D + s.rot_dim)
+        if self.q_latent:
+            self.w_q_down, self.w_q_up, self.q_norm_w = weights[s.q_down], weights[s.q_proj], weights[s.q_norm]
+        self.down_col = 0 if self.q_latent else H * (D + s.rot_dim)
         self.gate_col = self.down_col + R + s.rot_dim
+        self.gate_width = H if s.gate_per_head else H * V
         self.norm_w = weights[s.latent_norm]
         # UK_h^T as the matrix of a product x W^T: [heads, rank, dim]; UV_h as it is stored: [heads, vdim, rank]
         self.w_absorb = weights[s.k_up].view(H, D, R).transpose(1, 2).contiguous()
@@ -61,6 +68,19 @@ class LatentAttention:
         act = self.rt.act_dtype
         proj = ctx.buffer("la_proj", (n, self.w_in.shape[0]), torch.float32)
         k.linear(h, self.w_in, proj)
+        q = None
+        if self.q_latent:
+            cq_raw = ctx.buffer("la_cq_raw", (n, s.q_rank), torch.float32)
+            k.linear(h, self.w_q_down, cq_raw)
+            cq = ctx.buffer("la_cq", (n, s.q_rank), act)
+            k.rmsnorm(cq_raw, self.q_norm_w, s.eps, cq)
+            q = ctx.buffer("la_q", (n, H * (D + r)), torch.float32)
+            k.linear(cq, self.w_q_up, q)
+        extra = {}
+        if q is not None:
+            extra["q"] = q
+        if s.position is not None and s.position.interleaved:
+            extra["interleaved"] = True
         kv = ctx.kv(call.cache)
         lat_pages = kv.streams["latent"]
         rot_pages = kv.streams["rotated_key"] if r else None
@@ -72,7 +92,7 @@ class LatentAttention:
         tiles = ctx.buffer("la_tiles", (H * seg // tile,), torch.int32, rows=H * cap // tile) if tile else None
         table = self.position.table(ctx) if self.position is not None else None
         k.latent_prepare(proj, H, D, r, R, self.down_col, self.norm_w, s.eps, table, s.position.rotary_dim if table is not None else 0,
-                         q_plain, q_rot, lat_pages, rot_pages, kv.slot_mapping if call.store else None, offsets, tiles, tile)
+                         q_plain, q_rot, lat_pages, rot_pages, kv.slot_mapping if call.store else None, offsets, tiles, tile, **extra)
         q_lat = ctx.buffer("la_q_lat", (H * seg, R), torch.float32, rows=H * cap)
         if tile:
             k.moe_linear_grouped(q_plain.view(H * seg, D), self.w_absorb, tiles, q_lat)
@@ -88,8 +108,11 @@ class LatentAttention:
         else:
             k.moe_linear(o_lat, self.w_values, offsets, None, 1, y)
         out = ctx.buffer("la_out", (n, H * V), act)
-        gate = proj[:, self.gate_col:] if s.gate is not None else None
-        k.gate_heads(y.view(H, seg, V), gate, out, n)
+        gate = proj[:, self.gate_col:self.gate_col + self.gate_width] if s.gate is not None else None
+        if s.gate_per_head and gate is not None:
+            k.gate_heads(y.view(H, seg, V), gate, out, n, per_head=True)
+        else:
+            k.gate_heads(y.view(H, seg, V), gate, out, n)
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(out, self.w_o, delta)
         return delta

@@ -1,10 +1,11 @@
 """Recurrent mixers whose state lives in the request's state slot: the HGRN2 gated recurrence, retention with a fixed
-decay per head, RWKV-style time mixing (all three a matrix state per head) and the element-wise minGRU."""
+decay per head, RWKV-style time mixing (all three a matrix state per head), the element-wise minGRU and the real-gated
+linear recurrent unit behind a short convolution."""
 from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedRecurrenceSpec, GatedUnitSpec, RetentionSpec, TimeMixSpec
+from ..config.specs import GatedRecurrenceSpec, GatedUnitSpec, RealGatedRecurrenceSpec, RetentionSpec, TimeMixSpec
 from .registry import register_part
 
 
@@ -161,3 +162,70 @@ class GatedUnit:
 
 
 register_part(GatedUnitSpec, GatedUnit)
+
+
+class RealGatedRecurrence:
+    """h -> o_proj(S * gelu_tanh(Y h + by)), S <- a S + sqrt(1 - a^2) * i * u per channel, u = conv(X h + bx).
+
+    y | x run as one product into float32.  One kernel adds the x bias, runs the short causal convolution over each
+    request's tokens from the inputs its slot kept (cache entry 1) and writes u twice: float32 for the recurrence and, in the
+    products' dtype, block by block for the gates.  The two block-diagonal gate matrices are one grouped product (the
+    framework's grouped product with a block in an expert's place: r | i of a block are the rows of one matrix) into
+    float32.  The recurrence kernel adds the gates' biases, forms sigmoid, softplus, the decay and the input term in float32,
+    walks each request's tokens from the slot's state (cache entry 0; long portions in chunks side by side) and multiplies
+    by the gelu branch.  A prompt, a portion and a decoded token are the same calls: the slot carries the past."""
+
+    graph_safe = True
+
+    def __init__(self, spec: RealGatedRecurrenceSpec, weights, runtime):
+        self.spec = s = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        f32 = lambda name: weights[name].to(torch.float32).contiguous()      # small vectors: the kernels read float32
+        self.w_yx = torch.cat((weights[s.y_proj], weights[s.x_proj]), dim=0).contiguous()
+        self.y_bias, self.x_bias = f32(s.y_bias), f32(s.x_bias)
+        self.conv_w, self.conv_b = f32(s.conv), f32(s.conv_bias)
+        self.w_gates = torch.cat((weights[s.a_gate], weights[s.x_gate]), dim=1).contiguous()      # [blocks, 2 bs, bs]
+        self.a_bias, self.i_bias = f32(s.a_bias).reshape(-1), f32(s.x_bias_gate).reshape(-1)
+        self.decay = f32(s.decay)
+        self.w_o = weights[s.o_proj]
+
+    def _segment(self, n):
+        """Rows of a block's segment in the grouped product, and the tile of the tcgen05 route (0: the other route)."""
+        k = self.k
+        ok = getattr(k, "moe_grouped_tc_ok", None)
+        if ok is not None and ok(n * self.spec.blocks, self.rt.act_dtype, self.w_gates):
+            t = k.MOE_TILE
+            return -(-n // t) * t, t
+        return n, 0
+
+    def forward(self, h, ctx, call):
+        s, k = self.spec, self.k
+        n = h.shape[0]
+        W, B = s.width, s.blocks
+        bs = W // B
+        act = self.rt.act_dtype
+        proj = ctx.buffer("rg_proj", (n, 2 * W), torch.float32)
+        k.linear(h, self.w_yx, proj)
+        seg, tile = self._segment(n)
+        cap, _ = self._segment(ctx.max_rows)
+        u = ctx.buffer("rg_u", (n, W), torch.float32)
+        ub = ctx.buffer("rg_u_blocks", (B * seg, bs), act, rows=B * cap).view(B, seg, bs)
+        offsets = ctx.buffer("rg_offsets", (B + 1,), torch.int32, rows=B + 1)
+        tiles = ctx.buffer("rg_tiles", (B * seg // tile,), torch.int32, rows=B * cap // tile) if tile else None
+        k.rglru_conv(proj, W, self.x_bias, self.conv_w, self.conv_b, ctx.state((call.cache, 1)), ctx.state_slots, ctx.cu_q,
+                     ctx.seq_lens, ctx.req_index, u, ub, offsets, tiles, tile)
+        gates = ctx.buffer("rg_gates", (B * seg, 2 * bs), torch.float32, rows=B * cap)
+        if tile:
+            k.moe_linear_grouped(ub.view(B * seg, bs), self.w_gates, tiles, gates)
+        else:
+            k.moe_linear(ub.view(B * seg, bs), self.w_gates, offsets, None, 1, gates)
+        out = ctx.buffer("rg_out", (n, W), act)
+        k.rglru_scan(gates.view(B, seg, 2 * bs), self.a_bias, self.i_bias, self.decay, s.decay_scale, u, proj, 0, self.y_bias,
+                     ctx.state((call.cache, 0)), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, max_q_len=ctx.max_q_len)
+        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
+        k.linear(out, self.w_o, delta)
+        return delta
+
+
+register_part(RealGatedRecurrenceSpec, RealGatedRecurrence)

@@ -8,6 +8,26 @@ from ..errors import ModelConfigError
 from .registry import register_part
 
 
+def rotary_frequencies(spec: RotarySpec):
+    """(float32 frequencies of the rotated pairs, the factor on cosine and sine).  The frequencies are formed in
+    float64 and rounded once; with ``scaling`` the slow ones are stretched as the description says."""
+    import math
+    i = torch.arange(0, spec.rotary_dim // 2, dtype=torch.float64)
+    freq = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim)
+    gain = 1.0
+    if spec.scaling is not None:
+        factor, original, fast, slow = (float(v) for v in spec.scaling)
+
+        def dim_of(turns):
+            return spec.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(spec.theta))
+        lo = max(math.floor(dim_of(fast)), 0)
+        hi = min(math.ceil(dim_of(slow)), spec.rotary_dim - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        freq = freq / factor * ramp + freq * (1.0 - ramp)
+        gain = 0.1 * math.log(factor) + 1.0
+    return freq.to(torch.float32), float(gain)
+
+
 class Rotary:
     """inv_freq_i = 1 / theta^(2i / rotary_dim), angle = position * inv_freq_i, both in
     float32 (src/infurnace/executor/tinygrad/model.py:18-22); the rotation itself runs
@@ -21,25 +41,33 @@ class Rotary:
             raise ModelConfigError(f"rotary_dim {spec.rotary_dim} must be even and at most head_dim {spec.head_dim}")
         self.spec = spec
         self.k = runtime.kernels
-        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
-        self.inv_freq = (1.0 / (spec.theta ** exponent)).to(runtime.device)
+        freq, self.gain = rotary_frequencies(spec)
+        self.inv_freq = freq.to(runtime.device)
 
     def fused_rotary(self):
+        if self.gain != 1.0:
+            return None                       # the fused kernels form plain cosines and sines themselves
         return self.inv_freq, self.spec.rotary_dim, self.spec.interleaved
 
     def table(self, ctx):
         """(cos, sin) of every token's angles, computed once per step and shared by all layers with the same
         base and rotated width (the angles do not depend on the layer)."""
-        key = ("rope_table", self.spec.theta, self.spec.rotary_dim)
+        key = ("rope_table", self.spec.theta, self.spec.rotary_dim, self.spec.scaling)
         t = ctx.shared.get(key)
         if t is None:
-            t = ctx.buffer(f"rope_table_{self.spec.theta}_{self.spec.rotary_dim}", (ctx.num_tokens, self.spec.rotary_dim),
+            tag = "" if self.spec.scaling is None else "_" + "_".join(repr(v) for v in self.spec.scaling)
+            t = ctx.buffer(f"rope_table_{self.spec.theta}_{self.spec.rotary_dim}{tag}", (ctx.num_tokens, self.spec.rotary_dim),
                            torch.float32)
-            self.k.rope_table(ctx.positions, self.inv_freq, t)
+            if self.gain != 1.0:
+                self.k.rope_table(ctx.positions, self.inv_freq, t, gain=self.gain)
+            else:
+                self.k.rope_table(ctx.positions, self.inv_freq, t)
             ctx.shared[key] = t
         return t
 
     def apply(self, qkv, num_heads, num_kv_heads, head_dim, positions):
+        if self.gain != 1.0:
+            raise ModelConfigError("a rotation whose cosine and sine carry a factor runs from its per-step table only")
         self.k.qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, None, None, 0.0,
                                   self.inv_freq, self.spec.rotary_dim, self.spec.interleaved,
                                   positions, None, None)

@@ -10,7 +10,8 @@ from .registry import build_part, register_part
 class RotaryValueAttention:
     """h -> o_proj(unrotate(attention(q, K, V))).
 
-    q | k | v run as one product.  One kernel rotates the q and k heads on their first rotary_dim entries, divides
+    q | k | v run as one product (q | k where the description has no value projection: a value head is then its key head
+    as projected, before the rotation).  One kernel rotates the q and k heads on their first rotary_dim entries, divides
     each value head by its root mean square and rotates it over its whole width by the token's position, writes q
     in the cache's dtype and k and v into their page streams (which may differ in width).  The attention kernel reads
     every key and value from the pages, this step's included, keeps scores, softmax weights and sums in float32,
@@ -23,7 +24,11 @@ class RotaryValueAttention:
         self.spec = spec
         self.rt = runtime
         self.k = runtime.kernels
-        self.w_qkv = torch.cat([weights[n] for n in (spec.q_proj, spec.k_proj, spec.v_proj)], dim=0).contiguous()
+        self.values_are_keys = spec.v_proj is None
+        if self.values_are_keys and (spec.value_head_dim != spec.head_dim or spec.value_norm or spec.value_position is not None):
+            raise ValueError("values that are the keys have the keys' width, no norm and no rotation of their own")
+        names = (spec.q_proj, spec.k_proj) if self.values_are_keys else (spec.q_proj, spec.k_proj, spec.v_proj)
+        self.w_qkv = torch.cat([weights[n] for n in names], dim=0).contiguous()
         self.w_o = weights[spec.o_proj]
         self.position = build_part(spec.position, weights, runtime) if spec.position is not None else None
         self.value_position = build_part(spec.value_position, weights, runtime) if spec.value_position is not None else None
@@ -31,7 +36,8 @@ class RotaryValueAttention:
             raise ValueError("the values are rotated over their whole width")
         import os
         self.exact_weights = os.environ.get("INFURNACE_EXACT_ATTENTION", "0") not in ("", "0")
-        self.width = spec.num_heads * spec.head_dim + spec.num_kv_heads * (spec.head_dim + spec.value_head_dim)
+        self.width = spec.num_heads * spec.head_dim + spec.num_kv_heads * (
+            spec.head_dim + (0 if self.values_are_keys else spec.value_head_dim))
 
     def _on_tensor_cores(self, kv):
         """bfloat16 with keys and values of one width in one tensor: the framework's tensor-core attention kernels run
@@ -59,7 +65,7 @@ class RotaryValueAttention:
                        bool(s.position.interleaved) if s.position is not None else False,
                        s.eps if s.value_norm else None, v_table,
                        bool(s.value_position.interleaved) if s.value_position is not None else False,
-                       q, pk, pv, kv.slot_mapping if call.store else None)
+                       q, pk, pv, kv.slot_mapping if call.store else None, **({"values_are_keys": True} if self.values_are_keys else {}))
         out = ctx.buffer("rva_out", (n, s.num_heads * s.value_head_dim), self.rt.act_dtype)
         if self._on_tensor_cores(kv):
             # the framework's tensor-core attention over the entry's one tensor of keys and values, then the turn back

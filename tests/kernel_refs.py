@@ -102,10 +102,10 @@ class ReferenceKernels:
         partials[:parts].copy_(sq.view(v.shape[0], parts, 16).sum(dim=2).t().to(partials.dtype))
 
     # ------------------------------------------------------------------ q/k norm, rotation, store
-    def rope_table(self, positions, inv_freq, out):
-        """out[tok] = (cos, sin) pairs of positions[tok] * inv_freq[i], interleaved: [tokens, 2 * len(inv_freq)]."""
+    def rope_table(self, positions, inv_freq, out, gain=1.0):
+        """out[tok] = gain * (cos, sin) pairs of positions[tok] * inv_freq[i], interleaved: [tokens, 2 * len(inv_freq)]."""
         ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
-        out.copy_(torch.stack((ang.cos(), ang.sin()), dim=-1).flatten(-2))
+        out.copy_(torch.stack((ang.cos() * gain, ang.sin() * gain), dim=-1).flatten(-2))
 
     def qk_norm_rope_store(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps,
                            inv_freq, rotary_dim, interleaved, positions, slot_mapping, kv_pages, rope_table=None):
@@ -314,12 +314,14 @@ class ReferenceKernels:
             t = t + vec.to(self.cd)[None, :]
         x.copy_(t.to(x.dtype))
 
-    def scaled_sum(self, total, d, scale, accumulate=True):
-        """total (+)= scale * d."""
+    def scaled_sum(self, total, d, scale, accumulate=True, copy=None):
+        """total (+)= scale * d; ``copy`` also gets the new total."""
         t = d.to(self.cd) * scale
         if accumulate:
             t = t + total.to(self.cd)
         total.copy_(t.to(total.dtype))
+        if copy is not None:
+            copy.copy_(total.to(copy.dtype))
 
     def token_side_gate(self, z, table, ids, offset, activation, out):
         """out[n, j] = act(z[n, j]) * table[ids[n], offset + j]."""
@@ -403,6 +405,63 @@ class ReferenceKernels:
                 out[t] = (S * g * torch.sigmoid(g)).to(out.dtype)
             state[slot] = S.to(state.dtype)
 
+    # ------------------------------------------------------------------ the real-gated linear recurrent unit
+    def rglru_conv(self, proj, x_col, x_bias, conv_weight, conv_bias, state, state_slots, cu_q, seq_lens, req_index, u, u_blocks,
+                   offsets, tile_block=None, tile=0):
+        """u_t = conv_bias + sum_j conv_weight[:, j] * xin_(t - taps + 1 + j), xin = proj[:, x_col:x_col + width] + x_bias, per
+        request from the inputs its slot kept; u token-major float32 and block-major in u_blocks [blocks, seg, bs]."""
+        n, width = u.shape
+        blocks, seg, bs = u_blocks.shape
+        taps = conv_weight.shape[1]
+        K = taps - 1
+        xin = proj[:, x_col:x_col + width].to(self.cd) + x_bias.to(self.cd)
+        w, b = conv_weight.to(self.cd), conv_bias.to(self.cd)
+        offsets.copy_(torch.arange(blocks + 1, dtype=offsets.dtype) * seg)
+        if tile_block is not None:
+            tile_block.copy_((torch.arange(tile_block.numel()) // (seg // tile)).to(tile_block.dtype))
+        for r in range(seq_lens.numel()):
+            a, e = int(cu_q[r]), int(cu_q[r + 1])
+            if e == a:
+                continue
+            if int(seq_lens[r]) <= 0:
+                u[a:e] = 0
+                continue
+            st = state[int(state_slots[r])]
+            hist = torch.cat((st[:K].to(self.cd), xin[a:e]), dim=0) if K else xin[a:e]
+            acc = b.expand(e - a, width).clone()
+            for j in range(taps):
+                acc = acc + w[:, j] * hist[j:j + e - a]
+            u[a:e] = acc.to(u.dtype)
+            if K:
+                st[:K] = hist[hist.shape[0] - K:].to(st.dtype)
+        u_blocks[:, :n] = u.view(n, blocks, bs).transpose(0, 1).to(u_blocks.dtype)
+
+    def rglru_scan(self, gates, a_bias, i_bias, decay, decay_scale, u, proj, y_col, y_bias, state, state_slots, cu_q, seq_lens, out,
+                   max_q_len=1):
+        """r = sigmoid(gates_r + a_bias), i = sigmoid(gates_i + i_bias), a = exp(-decay_scale * r * softplus(decay)),
+        S <- a S + sqrt(1 - a^2) * i * u from the slot's state; out = S * gelu_tanh(proj[:, y_col:y_col + width] + y_bias)."""
+        n, width = out.shape
+        blocks, seg, two_bs = gates.shape
+        bs = two_bs // 2
+        g = gates[:, :n].to(self.cd)
+        r = torch.sigmoid(g[..., :bs].transpose(0, 1).reshape(n, width) + a_bias.to(self.cd))
+        i = torch.sigmoid(g[..., bs:].transpose(0, 1).reshape(n, width) + i_bias.to(self.cd))
+        loga = -decay_scale * r * torch.nn.functional.softplus(decay.to(self.cd))
+        a = torch.exp(loga)
+        term = torch.sqrt(torch.clamp(-torch.expm1(2 * loga), min=0)) * i * u.to(self.cd)
+        y = torch.nn.functional.gelu(proj[:, y_col:y_col + width].to(self.cd) + y_bias.to(self.cd), approximate="tanh")
+        for q in range(seq_lens.numel()):
+            lo, hi = int(cu_q[q]), int(cu_q[q + 1])
+            if int(seq_lens[q]) <= 0:
+                out[lo:hi] = 0
+                continue
+            S = state[int(state_slots[q])].to(self.cd)
+            for t in range(lo, hi):
+                S = a[t] * S + term[t]
+                out[t] = (S * y[t]).to(out.dtype)
+            if hi > lo:
+                state[int(state_slots[q])] = S.to(state.dtype)
+
     # ------------------------------------------------------------------ attention with rotated values
     @staticmethod
     def _turn(t, cos, sin, dims, interleaved):
@@ -421,15 +480,15 @@ class ReferenceKernels:
         return pairs[..., 0][:, None, :], pairs[..., 1][:, None, :]
 
     def rotary_store(self, qkv, num_heads, num_kv_heads, head_dim, value_head_dim, qk_table, rotary_dim, interleaved, value_eps,
-                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping):
-        """qkv [n, H d + G d + G dv].  q and k are rotated by the angles of qk_table ([n, rotary_dim] (cos, sin)
+                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping, values_are_keys=False):
+        """qkv [n, H d + G d + G dv] ([n, H d + G d] with ``values_are_keys``: a value head is its key head before rotation).  q and k are rotated by the angles of qk_table ([n, rotary_dim] (cos, sin)
         pairs; None: not rotated); each value head is divided by its root mean square (value_eps None: not) and
         rotated over its whole width by v_table (None: not).  q_out gets q; k and v go to their pages
         [pages, G, page_size, width] at slot_mapping (None: nothing is stored)."""
         n, H, G, d, dv = qkv.shape[0], num_heads, num_kv_heads, head_dim, value_head_dim
         q = qkv[:, : H * d].to(self.cd).reshape(n, H, d)
         k = qkv[:, H * d: (H + G) * d].to(self.cd).reshape(n, G, d)
-        v = qkv[:, (H + G) * d:].to(self.cd).reshape(n, G, dv)
+        v = k.clone() if values_are_keys else qkv[:, (H + G) * d:].to(self.cd).reshape(n, G, dv)
         if qk_table is not None:
             c, s_ = self._table(qk_table)
             q, k = self._turn(q, c, s_, rotary_dim, interleaved), self._turn(k, c, s_, rotary_dim, interleaved)
@@ -486,6 +545,11 @@ class ReferenceKernels:
         experts, limited to the ``keep`` groups of neighbours with the largest best score when ``groups`` = (count, keep);
         gates[n] = score * weight_scale.  Only the first ``experts`` columns of ``logits`` are the router's."""
         z = logits[:, :experts if experts is not None else logits.shape[1]].to(self.cd)
+        if scoring == "sigmoid":         # sigmoid(z) per expert; the order of the logits is the order of the scores
+            val, idx = torch.sort(z, dim=-1, descending=True, stable=True)
+            ids.copy_(idx[:, :top].to(ids.dtype))
+            gates.copy_((torch.sigmoid(val[:, :top]) * weight_scale).to(gates.dtype))
+            return
         if scoring == "chosen":
             val, idx = torch.sort(z, dim=-1, descending=True, stable=True)
             ids.copy_(idx[:, :top].to(ids.dtype))
@@ -538,8 +602,19 @@ class ReferenceKernels:
                 raise ValueError(epilogue)
             out[a:b] = y.to(out.dtype)
 
+    def moe_gather_scaled(self, x, perm, top, gates, out, tile_expert=None):
+        """out[place] = gates[perm[place]] * x[perm[place] // top], zeros where perm[place] < 0."""
+        p = perm.long()
+        live = p >= 0
+        rows = torch.zeros(out.shape, dtype=self.cd)
+        rows[live] = x[p[live] // top].to(self.cd) * gates.reshape(-1)[p[live]].to(self.cd)[:, None]
+        out.copy_(rows.to(out.dtype))
+
     def moe_combine(self, y, pos, gates, out, shared=None, shared_logit=None):
-        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending; + shared[n] (times sigmoid(shared_logit[n]))."""
+        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending (gates None: weights of 1); + shared[n] (times
+        sigmoid(shared_logit[n]))."""
+        if gates is None:
+            gates = torch.ones(out.shape[0], pos.numel() // max(out.shape[0], 1), dtype=self.cd)
         n, top = gates.shape
         acc = torch.zeros(n, y.shape[1], dtype=self.cd)
         for j in range(top):
@@ -599,12 +674,12 @@ class ReferenceKernels:
                 state[slot, :K] = seq[seq.shape[0] - K:].to(state.dtype)
 
     def latent_prepare(self, proj, heads, dim, rot, rank, down_col, norm_weight, eps, table, dims, q_plain, q_rot, latent_pages,
-                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0):
+                       rot_pages, slot_mapping, offsets, tile_head=None, tile=0, q=None, interleaved=False):
         """Queries head-major, rotated parts turned, the normalised latent and the turned shared key part into the pages."""
         n = proj.shape[0]
         seg = q_plain.shape[1]
         p = proj.to(self.cd)
-        q = p[:, :heads * (dim + rot)].view(n, heads, dim + rot)
+        q = (p[:, :heads * (dim + rot)] if q is None else q.to(self.cd)).reshape(n, heads, dim + rot)
         q_plain[:, :n] = q[..., :dim].transpose(0, 1).to(q_plain.dtype)
         offsets.copy_(torch.arange(heads + 1, dtype=offsets.dtype) * seg)
         if tile_head is not None:
@@ -617,6 +692,11 @@ class ReferenceKernels:
             while cs.dim() < v.dim() + 1:
                 cs = cs.unsqueeze(1)
             c, s = cs[..., 0], cs[..., 1]
+            if interleaved:
+                a, b = v[..., 0:dims:2], v[..., 1:dims:2]
+                w = v.clone()
+                w[..., 0:dims:2], w[..., 1:dims:2] = a * c - b * s, b * c + a * s
+                return w
             a, b = v[..., :dims // 2], v[..., dims // 2:dims]
             return torch.cat((a * c - b * s, b * c + a * s, v[..., dims:]), dim=-1)
 
@@ -664,12 +744,13 @@ class ReferenceKernels:
                     den = den + torch.exp(sink.to(self.cd) - m)
                 out[:, t] = ((e / den[:, None]) @ c).to(out.dtype)
 
-    def gate_heads(self, y, gate, out, tokens):
-        """out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v])."""
+    def gate_heads(self, y, gate, out, tokens, per_head=False):
+        """out[t, h * vdim + v] = y[h, t, v] * sigmoid(gate[t, h * vdim + v]) (``per_head``: gate[t, h])."""
         heads, seg, vdim = y.shape
         v = y[:, :tokens].to(self.cd).transpose(0, 1).reshape(tokens, heads * vdim)
         if gate is not None:
-            v = v * torch.sigmoid(gate.to(self.cd))
+            g = torch.sigmoid(gate.to(self.cd))
+            v = v * (g.repeat_interleave(vdim, dim=1) if per_head else g)
         out.copy_(v.to(out.dtype))
 
     # ------------------------------------------------------------------ sampling
