@@ -657,10 +657,49 @@ def latent_config(size):
             "residual_mult": 0.5, "vocab": 32768, "width": W}
 
 
+def recurrent_config(size):
+    """A Golonex config.json mapping at the width, depth, head count and ACTIVE parameter count of hybrid_config(size):
+    layers latent attention, latent attention, attention whose values are its keys, real-gated recurrence, and again;
+    latent attention with heads of the attention's size, a latent of twice and a rotated part of a quarter of it, queries
+    through a latent of half the width, a window, sinks and a gate per head; attention rotated on half of each head with
+    stretched frequencies under the same window; a recurrence as wide as the model in blocks of 128 channels with four
+    taps; 8 experts of which 2 run, each a sixth of the dense feed-forward's width, beside a shared expert of a third; a
+    token side input of 32 and a soft cap."""
+    W, layers, H, G, d, _, _, _, ff, window = {
+        "s": (1024, 8, 16, 4, 64, 8, 64, 128, 3072, 512),
+        "m": (2048, 8, 16, 4, 128, 16, 64, 128, 6144, 1024),
+        "l": (4096, 8, 32, 8, 128, 32, 64, 128, 12288, 1024),
+    }[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff // 3}, "router": {"experts": 8, "top": 2}}
+    entries = []
+    for i in range(layers):
+        if i % 4 in (0, 1):
+            entries.append({"type": "latent_attention", "mlp": mlp, "mixer": {
+                "heads": H, "dim": d, "rot_dim": d // 4, "vdim": d, "kv_rank": 2 * d, "q_rank": W // 2, "scale": (d + d // 4) ** -0.5,
+                "rot": {"base": 1e6, "dims": d // 4}, "mask": {"size": window}}})
+        elif i % 4 == 2:
+            entries.append({"type": "attention", "mlp": mlp, "mixer": {
+                "heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": window},
+                "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}})
+        else:
+            entries.append({"type": "rglru", "mlp": mlp, "mixer": {"width": W, "blocks": W // 128, "conv": 4}})
+    return {"architecture": "Golonex", "layers": entries, "norm": {"eps": 1e-6}, "vocab": 32768, "width": W,
+            "token_side": {"dim": 32}, "logit_softcap": 30.0}
+
+
+def window_pairs(window, positions):
+    """Sum over query positions of the keys each sees under a sliding window."""
+    return sum(min(p + 1, window) for p in positions)
+
+
 def attention_shape(conf):
     """(key/value heads, head size, chunk or None) of a design's attention layers, from its config.json mapping."""
     if "layers" not in conf:
         return conf["num_key_value_heads"], conf["head_dim"], None
+    if conf.get("architecture") == "Golonex":             # a window, not a chunk: the caller counts its pairs
+        for layer in conf["layers"]:
+            if layer["type"] == "attention":
+                return layer["mixer"]["kv_heads"], layer["mixer"]["dim"], None
     for layer in conf["layers"]:
         m = layer["mixer"]
         if layer["type"] == "attention":
@@ -682,7 +721,7 @@ class DesignTimer(KernelClassTimer):
                                           "rotate_rows", "paged_attention_streams", "moe_route", "moe_plan", "moe_linear",
                                           "moe_combine", "moe_plan_padded", "moe_gather", "moe_linear_grouped", "moe_route_plan",
                                           "group_rmsnorm", "depth_average", "causal_conv", "latent_prepare", "latent_attention",
-                                          "gate_heads")
+                                          "gate_heads", "rglru_conv", "rglru_scan", "moe_gather_scaled")
 
     def __init__(self, kernels, vocab, pairs, key_bytes, positions=(), head_weights=()):
         super().__init__(kernels, vocab)
@@ -714,6 +753,11 @@ class DesignTimer(KernelClassTimer):
         elif name == "gated_unit_scan":
             proj, out = a[0], a[7]
             cls, ff, by = "recurrence", 10 * out.numel(), proj.numel() * 4 + out.numel() * out.element_size()
+        elif name == "rglru_scan":
+            gates, u, out = a[0], a[5], a[13]
+            # the least: the gates' two numbers, u and the gelu branch's input read once, the result written; per element
+            # two sigmoids, two exponentials, a root, a tanh and a dozen products and sums
+            cls, ff, by = "recurrence", 40 * out.numel(), out.numel() * (4 * 4 + out.element_size())
         elif name == "latent_attention":
             q_lat, lat_pages, rot_pages, window = a[0], a[2], a[3], a[11]
             H, _, R = q_lat.shape
@@ -793,6 +837,8 @@ def run_designs(args):
         pair = (("lunelorn", hybrid_config(size)), ("kafunex", kaf)) if args.hybrid else (("kafunex", kaf), ("qwen3", qwen))
         if args.latent:
             pair = (("filorax", latent_config(size)), ("lunelorn", hybrid_config(size)))
+        if args.recurrent:
+            pair = (("golonex", recurrent_config(size)), ("lunelorn", hybrid_config(size)))
         for design, conf in pair:
             pool = batch * (context + 64) + PREFILL_TOKENS + 64
             opts = EngineOptions(dtype="bfloat16", page_size=16, num_pages=pool // 16, max_num_seqs=batch,
@@ -815,10 +861,14 @@ def run_designs(args):
             K = runner.rt.kernels
             graphs, runner.use_graphs = runner.use_graphs, False
             mixers = [getattr(layer, "mixer", None) for layer in runner.model.layers]
-            heads_w = [w.data_ptr() for m in mixers for w in (getattr(m, "w_absorb", None), getattr(m, "w_values", None)) if w is not None]
+            heads_w = [w.data_ptr() for m in mixers for w in (getattr(m, "w_absorb", None), getattr(m, "w_values", None),
+                                                             getattr(m, "w_gates", None)) if w is not None]
+            window = next((layer["mixer"]["mask"]["size"] for layer in conf.get("layers", ()) if design == "golonex"
+                           and layer["type"] == "attention" and layer["mixer"].get("mask")), None)
+            pairs_of = (lambda positions: window_pairs(window, positions)) if window else (lambda positions: visible_pairs(chunk, positions))
             toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(2)).tolist()
             runner.cache.add_request("kp")
-            with DesignTimer(K, vocab, visible_pairs(chunk, range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2,
+            with DesignTimer(K, vocab, pairs_of(range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2,
                              positions=range(PREFILL_TOKENS), head_weights=heads_w) as t:
                 torch.cuda.synchronize()
                 hold_the_device(20.0)
@@ -829,7 +879,7 @@ def run_designs(args):
             zeros = [0.0] * batch
             step = lambda: runner.step_and_sample([StepEntry(x, [1], [0]) for x in rids], zeros, zeros)      # noqa: E731
             step()
-            seen = visible_pairs(chunk, [context + 1])          # keys a decoded token sees
+            seen = pairs_of([context + 1])          # keys a decoded token sees
             with DesignTimer(K, vocab, batch * seen, batch * seen * G_ * d_ * 2 * 2, positions=[context + 1] * batch,
                              head_weights=heads_w) as t:
                 for _ in range(3):
@@ -1032,6 +1082,8 @@ def main():
                     help="with --designs: the Lunelorn design beside Kafunex (equal width, depth and active parameters)")
     ap.add_argument("--latent", action="store_true",
                     help="with --designs: the Filorax design beside Lunelorn (equal width, depth and active parameters)")
+    ap.add_argument("--recurrent", action="store_true",
+                    help="with --designs: the Golonex design beside Lunelorn (equal width, depth and active parameters)")
     ap.add_argument("--design-sizes", default="s,m", help="with --designs: which of the sizes s, m, l (commas between)")
     ap.add_argument("--kernels-alone", action="store_true",
                     help="with --designs: only the talking attention and the gated recurrence, each alone (a small case)")

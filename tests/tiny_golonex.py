@@ -75,7 +75,7 @@ TINY = {
         _rec(192, 4, 4, _moe(4, 3, 128, shared=64)),
         _att(8, 2, 64, 0.12, 50, 10000.0, 32, _moe(8, 1, 32), scaling=(2.0, 256, 16.0, 1.0)),
         _lat(8, 16, 16, 16, 96, 48, 0.3, 120, 20000.0, None)], cap=12.0, side=16),
-               page_size=16, store="bfloat16", seed=33),
+               page_size=16, store="bfloat16", seed=33, sharpen=2.0),       # run in bfloat16 over hundreds of tokens
 }
 
 
@@ -94,7 +94,8 @@ def make_weights(cfg, seed, sharpen=3.0):
     def vec(size, spread):
         return spread * torch.randn(size, generator=g)
 
-    w = {"embed": torch.randn(V, W, generator=g), "embed.norm": near_one(W), "final.norm": near_one(W)}
+    # the table is also the head: rows of length two keep the logits of size two (the embedding's norm undoes the scale)
+    w = {"embed": mat(V, W, 2.0), "embed.norm": near_one(W), "final.norm": near_one(W)}
     if side is not None:
         w["side.embed"] = torch.randn(V, n * side, generator=g)
     for i, layer in enumerate(cfg["layers"]):
@@ -136,7 +137,7 @@ def make_weights(cfg, seed, sharpen=3.0):
     return w
 
 
-def make_model_dir(name, root, config=None, seed=None, store=None):
+def make_model_dir(name, root, config=None, seed=None, store=None, sharpen=None):
     """Write tiny model ``name`` under ``root`` (config.json, model.safetensors) and return the folder.  The values
     are rounded to the storage dtype before they are written, so the oracle and the engine read the same numbers."""
     from safetensors.torch import save_file
@@ -147,7 +148,8 @@ def make_model_dir(name, root, config=None, seed=None, store=None):
     with open(os.path.join(d, "config.json"), "w") as f:
         json.dump(config, f)
     dt = getattr(torch, store or spec["store"])
-    save_file({k: v.to(dt).contiguous() for k, v in make_weights(config, seed if seed is not None else spec["seed"]).items()},
+    made = make_weights(config, seed if seed is not None else spec["seed"], sharpen=sharpen or spec.get("sharpen", 3.0))
+    save_file({k: v.to(dt).contiguous() for k, v in made.items()},
               os.path.join(d, "model.safetensors"))
     return d
 
