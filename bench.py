@@ -852,11 +852,12 @@ def run_designs(args):
             pre = statistics.median(ms)
             rids = fill_contexts(runner, batch, context)
             randomize_pages(runner)
-            total, launches, per = time_decode(runner, rids, vocab, args.steps, max(3, args.warmup))
+            steps = min(args.steps, 48)                     # a request has room for 64 more tokens
+            total, launches, per = time_decode(runner, rids, vocab, steps, max(3, args.warmup))
             release(runner, rids)
             dec = statistics.median(per)
             r = {"params_m": round(params / 1e6, 1), "prefill_ms": round(pre, 3), "prefill_tok_s": round(PREFILL_TOKENS / pre * 1e3),
-                 "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3), "decode_launches": launches // args.steps}
+                 "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3), "decode_launches": launches // steps}
             # where the time goes: an eager pass with events around every launch
             K = runner.rt.kernels
             graphs, runner.use_graphs = runner.use_graphs, False
@@ -1061,6 +1062,84 @@ def time_hybrid_kernels(args):
     return 0
 
 
+def time_recurrent_kernels(args):
+    """The real-gated recurrence's kernels each alone (its convolution, the block-diagonal gate product, the walk), beside
+    the element-wise recurrence of the closest design (minGRU) at the same width: a 2,048-token prompt in one step and a
+    decode step of 8 requests, CUDA events over 20 repetitions, against the bytes each has to move at the least over the
+    measured copy bandwidth; one JSON line.  (Also the small case for a profiler.)"""
+    import torch
+    from infurnace_b200.kernels import load_cuda_kernels
+    K = load_cuda_kernels()
+    hbm_peak, tc_peak, peak_src = read_peaks()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, generator=g, device="cuda").to(dtype)      # noqa: E731
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")                # larger than L2
+
+    def timed(f, reps=20):
+        for _ in range(3):
+            f()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            f()
+            e.record()
+            torch.cuda.synchronize()
+            total += s.elapsed_time(e)
+        return total / reps * 1e3
+
+    def entry(us, tf=0.0, by=0.0):
+        bound = max(tf / (tc_peak * 1e12), by / (hbm_peak * 1e9)) * 1e6
+        return {"us": round(us, 1), "of_bound": round(bound / us, 4)}
+
+    out = {}
+    for size in args.design_sizes.split(","):
+        conf = recurrent_config(size)
+        m = next(l["mixer"] for l in conf["layers"] if l["type"] == "rglru")
+        W, B, taps = m["width"], m["blocks"], m["conv"]
+        bs = W // B
+        xb, cw, cb = rnd(W), rnd(W, taps), rnd(W)
+        ab, ib, yb, lam = rnd(W), rnd(W), rnd(W), rnd(W) - 3
+        wg = rnd(B, 2 * bs, bs, dtype=torch.bfloat16) / 8
+        zb, xb2 = rnd(W), rnd(W)
+        r = {}
+        for label, lens in (("prompt_2048", [2048]), ("decode_8", [1] * 8)):
+            n = sum(lens)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+            seq = torch.tensor([x + 5 for x in lens], dtype=torch.int32, device="cuda")
+            slots = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+            req = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32, device="cuda"), torch.tensor(lens, device="cuda"))
+            req = req.to(torch.int32)
+            tile = K.MOE_TILE if K.moe_grouped_tc_ok(n * B, torch.bfloat16, wg) else 0
+            seg = -(-n // tile) * tile if tile else n
+            proj, u = rnd(n, 2 * W), torch.zeros(n, W, device="cuda")
+            ub = torch.zeros(B, seg, bs, dtype=torch.bfloat16, device="cuda")
+            off = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
+            tiles = torch.zeros(B * seg // tile, dtype=torch.int32, device="cuda") if tile else None
+            cstate, state = torch.zeros(8, max(taps - 1, 1), W, device="cuda"), torch.zeros(8, W, device="cuda")
+            gates = torch.zeros(B * seg, 2 * bs, device="cuda")
+            o = torch.zeros(n, W, dtype=torch.bfloat16, device="cuda")
+            r["convolution_" + label] = entry(timed(lambda: K.rglru_conv(proj, W, xb, cw, cb, cstate, slots, cu, seq, req, u, ub, off,
+                                                                         tiles, tile)), by=n * W * (4 + 4 + 2))
+            if tile:
+                f = lambda: K.moe_linear_grouped(ub.view(B * seg, bs), wg, tiles, gates)      # noqa: E731
+            else:
+                f = lambda: K.moe_linear(ub.view(B * seg, bs), wg, off, None, 1, gates)      # noqa: E731
+            r["gate_product_" + label] = entry(timed(f), tf=2.0 * n * B * 2 * bs * bs, by=n * W * (2 + 8) + wg.numel() * 2)
+            r["recurrence_" + label] = entry(timed(lambda: K.rglru_scan(gates.view(B, seg, 2 * bs), ab, ib, lam, 8.0, u, proj, 0, yb, state,
+                                                                        slots, cu, seq, o, max_q_len=max(lens))), by=n * W * 18)
+            proj3, ustate = rnd(n, 3 * W), torch.zeros(8, W, device="cuda")
+            r["gated_unit_" + label] = entry(timed(lambda: K.gated_unit_scan(proj3, zb, xb2, ustate, slots, cu, seq, o, max_q_len=max(lens))),
+                                             by=n * W * 14)
+        out[size] = r
+    K.check_device_errors()
+    print(json.dumps({"metric": "recurrent_kernels_alone", "dtype": "bfloat16 operands, float32 recurrences",
+                      "config": "L2 flushed between repetitions", "peaks": {"hbm_gbs": hbm_peak, "tensor_tflops": tc_peak, "source": peak_src},
+                      "sizes": out}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1099,6 +1178,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.designs:
         if args.kernels_alone:
+            if args.recurrent:
+                return time_recurrent_kernels(args)
             return time_hybrid_kernels(args) if args.hybrid else time_design_kernels(args)
         return run_designs(args)
     return run_ours(args)

@@ -55,14 +55,15 @@ def _check_mixer(kind, m, where):
     if kind == LATENT:
         for key in ("heads", "dim", "vdim", "kv_rank", "q_rank"):
             _int(m, key, where)
-        rot_dim = _int(m, "rot_dim", where, least=0)
+        rot_dim = _int(m, "rot_dim", where, least=0) if m.get("rot_dim") is not None else 0
         if rot_dim:
             _check_rot(m, where, rot_dim)
         return
     heads, kv = _int(m, "heads", where), _int(m, "kv_heads", where)
     if heads % kv:
         raise ModelConfigError(f"config.json: {where}heads {heads} is not a multiple of kv_heads {kv}")
-    dim, vdim = _int(m, "dim", where), _int(m, "vdim", where)
+    dim = _int(m, "dim", where)
+    vdim = _int(m, "vdim", where) if m.get("vdim") is not None else dim
     if vdim != dim:
         raise ModelConfigError(f"config.json: {where}vdim {vdim} differs from dim {dim}, but this mixer's values are its keys")
     if m.get("rot") is not None:

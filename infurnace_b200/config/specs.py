@@ -126,12 +126,15 @@ class RotarySpec:
     d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
     hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
     turns at inv_freq_i / factor * ramp_i + inv_freq_i * (1 - ramp_i), and cosine and sine are both
-    multiplied by 0.1 * ln(factor) + 1."""
+    multiplied by 0.1 * ln(factor) + 1.  ``frequency_dtype`` "float32": theta^(-2i/rotary_dim) is formed in float32, as
+    the reference forms it (model.py:18-22); "float64": formed in float64 and rounded to float32 once (always so with
+    ``scaling``)."""
     head_dim: int
     rotary_dim: int
     theta: float
     interleaved: bool = False
     scaling: Optional[Tuple[float, float, float, float]] = None
+    frequency_dtype: str = "float32"
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         return {}

@@ -32,7 +32,7 @@ DECAY_SCALE = 8.0              # log a = -8 * r * softplus(lam)
 def _rotary(rot, width):
     sc = rot.get("scaling")
     scaling = (float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None
-    return RotarySpec(width, int(rot["dims"]), float(rot["base"]), interleaved=True, scaling=scaling)
+    return RotarySpec(width, int(rot["dims"]), float(rot["base"]), interleaved=True, scaling=scaling, frequency_dtype="float64")
 
 
 def _window(m):
@@ -55,7 +55,7 @@ def _mixer(kind, m, p, W, eps):
             gate_per_head=True, q_rank=m["q_rank"], q_down=p + "dq", q_norm=p + "dq.norm")
     assert kind == ATTENTION
     return RotaryValueAttentionSpec(
-        hidden_size=W, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"], value_head_dim=m["vdim"],
+        hidden_size=W, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"], value_head_dim=m["dim"],
         scale=float(m["scale"]), eps=eps, q_proj=p + "q", k_proj=p + "k", v_proj=None, o_proj=p + "o",
         position=_rotary(m["rot"], m["dim"]) if m.get("rot") else None, window=_window(m))
 

@@ -9,9 +9,12 @@ from .registry import register_part
 
 
 def rotary_frequencies(spec: RotarySpec):
-    """(float32 frequencies of the rotated pairs, the factor on cosine and sine).  The frequencies are formed in
-    float64 and rounded once; with ``scaling`` the slow ones are stretched as the description says."""
+    """(float32 frequencies of the rotated pairs, the factor on cosine and sine).  With ``scaling`` the slow ones are
+    stretched as the description says."""
     import math
+    if spec.scaling is None and spec.frequency_dtype == "float32":
+        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
+        return 1.0 / (spec.theta ** exponent), 1.0
     i = torch.arange(0, spec.rotary_dim // 2, dtype=torch.float64)
     freq = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim)
     gain = 1.0
@@ -52,10 +55,11 @@ class Rotary:
     def table(self, ctx):
         """(cos, sin) of every token's angles, computed once per step and shared by all layers with the same
         base and rotated width (the angles do not depend on the layer)."""
-        key = ("rope_table", self.spec.theta, self.spec.rotary_dim, self.spec.scaling)
+        key = ("rope_table", self.spec.theta, self.spec.rotary_dim, self.spec.scaling, self.spec.frequency_dtype)
         t = ctx.shared.get(key)
         if t is None:
             tag = "" if self.spec.scaling is None else "_" + "_".join(repr(v) for v in self.spec.scaling)
+            tag += "" if self.spec.frequency_dtype == "float32" else "_" + self.spec.frequency_dtype
             t = ctx.buffer(f"rope_table_{self.spec.theta}_{self.spec.rotary_dim}{tag}", (ctx.num_tokens, self.spec.rotary_dim),
                            torch.float32)
             if self.gain != 1.0:
