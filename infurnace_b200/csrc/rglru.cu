@@ -9,15 +9,35 @@
 // (2) rglru_scan: per channel of a float32 state, r = sigmoid(gr + a_bias), i = sigmoid(gi + i_bias) from the gate products'
 // float32 results (block-major rows of [r | i]), log a = -scale * r * softplus(lam), a = exp(log a),
 // S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu_tanh(y_raw + y_bias).  A thread owns a (request, channel) and walks the
-// request's tokens of the step from the slot's state.  Long portions are cut into chunks of 64 tokens that run side by
-// side in two launches: the first forms every chunk's map S -> A S + B from zero and sets the slot's state aside, the
+// request's tokens of the step from the slot's state, eight tokens' numbers formed ahead of the chain.  Long portions are
+// cut into chunks of 32 tokens that run side by side in two launches: the first forms every chunk's map S -> A S + B from zero and sets the slot's state aside, the
 // second folds the maps of the chunks before its own onto that state, walks its chunk and writes the outputs (the last
 // chunk of a request writes the state).  The two forms differ by rounding only.  Everything here is float32 arithmetic.
 #include "common.cuh"
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------ the convolution
-template <typename TB>
+// A block is (token, slice of 128 * V channels); a thread owns V neighbouring channels (V = 4 where widths and addresses
+// allow 16-byte accesses, else 1).
+template <int V> struct RgVec { float v[V]; };
+template <int V> __device__ __forceinline__ RgVec<V> rg_load(const float* p) {
+  RgVec<V> r;
+  if constexpr (V == 4) { const float4 f = *reinterpret_cast<const float4*>(p); r.v[0] = f.x; r.v[1] = f.y; r.v[2] = f.z; r.v[3] = f.w; }
+  else r.v[0] = *p;
+  return r;
+}
+template <int V> __device__ __forceinline__ void rg_store(float* p, const RgVec<V>& r) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else *p = r.v[0];
+}
+template <int V> __device__ __forceinline__ void rg_store(__nv_bfloat16* p, const RgVec<V>& r) {
+  if constexpr (V == 4) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  } else *p = __float2bfloat16(r.v[0]);
+}
+
+template <typename TB, int V>
 __global__ void __launch_bounds__(128)
 rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const float* __restrict__ x_bias,
                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, float* __restrict__ state,
@@ -27,49 +47,60 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const int t = blockIdx.x;
-  if (t == 0) {
+  if (t == 0 && blockIdx.y == 0) {
     for (int b = threadIdx.x; b <= blocks; b += blockDim.x) offsets[b] = b * seg;
     if (tile_block != nullptr) {
       const int per = seg / tile;
       for (int j = threadIdx.x; j < blocks * per; j += blockDim.x) tile_block[j] = j / per;
     }
   }
+  const int e = (blockIdx.y * blockDim.x + threadIdx.x) * V;      // this thread's first channel
+  if (e >= width) return;
   const int bs = width / blocks;
   const int r = req_index[t];
   const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
+  TB* ub_e = ub + ((size_t)(e / bs) * seg) * bs + e % bs;          // + row * bs: the V channels lie in one block (bs % V == 0)
   if (seq_lens[r] <= 0) {                              // a padding row of a recorded step: it stores and sees nothing
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-      u[(size_t)t * width + e] = 0.f;
-      ub[((size_t)(e / bs) * seg + t) * bs + e % bs] = from_f32<TB>(0.f);
-    }
+    RgVec<V> z;
+#pragma unroll
+    for (int v = 0; v < V; ++v) z.v[v] = 0.f;
+    rg_store<V>(u + (size_t)t * width + e, z);
+    rg_store<V>(ub_e + (size_t)t * bs, z);
     return;
   }
   const int K = taps - 1, Kp = K > 0 ? K : 1;
   if (i > 0 && i < K) return;                          // the block of the portion's first token computes these
-  float* st = state + (size_t)state_slots[r] * Kp * width;
-  const float* xr = proj + x_col;
-  // input idx of the portion (negative: from the state), channel e
-  auto input = [&](int idx, int e) -> float {
-    return idx >= 0 ? xr[(size_t)(q0 + idx) * ld + e] + x_bias[e] : st[(size_t)(K + idx) * width + e];
+  float* st = state + (size_t)state_slots[r] * Kp * width + e;
+  const float* xr = proj + x_col + e;
+  const RgVec<V> xb = rg_load<V>(x_bias + e), cb = rg_load<V>(conv_b + e);
+  // input idx of the portion (negative: from the state)
+  auto input = [&](int idx) -> RgVec<V> {
+    if (idx < 0) return rg_load<V>(st + (size_t)(K + idx) * width);
+    RgVec<V> x = rg_load<V>(xr + (size_t)(q0 + idx) * ld);
+#pragma unroll
+    for (int v = 0; v < V; ++v) x.v[v] += xb.v[v];
+    return x;
   };
-  auto token = [&](int ii, int e) {
-    float acc = conv_b[e];
-    for (int j = 0; j <= K; ++j) acc = fmaf(conv_w[(size_t)e * taps + j], input(ii - K + j, e), acc);
-    u[(size_t)(q0 + ii) * width + e] = acc;
-    ub[((size_t)(e / bs) * seg + q0 + ii) * bs + e % bs] = from_f32<TB>(acc);
+  auto token = [&](int ii) {
+    RgVec<V> acc = cb;
+    for (int j = 0; j <= K; ++j) {
+      const RgVec<V> x = input(ii - K + j);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc.v[v] = fmaf(__ldg(conv_w + (size_t)(e + v) * taps + j), x.v[v], acc.v[v]);
+    }
+    rg_store<V>(u + (size_t)(q0 + ii) * width + e, acc);
+    rg_store<V>(ub_e + (size_t)(q0 + ii) * bs, acc);
   };
   if (i >= K) {                                        // reads this step's rows only
-    for (int e = threadIdx.x; e < width; e += blockDim.x) token(i, e);
+    token(i);
     return;
   }
   // i == 0 and K > 0: the tokens that read the state, then the state's replacement; a channel is one thread's throughout
   const int lim = len < K ? len : K;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    for (int ii = 0; ii < lim; ++ii) token(ii, e);
-    for (int k = 0; k < K; ++k) {                      // new entry k is the input at portion index len - K + k
-      const int src = len - K + k;
-      st[(size_t)k * width + e] = src >= 0 ? xr[(size_t)(q0 + src) * ld + e] + x_bias[e] : st[(size_t)(k + len) * width + e];
-    }
+  for (int ii = 0; ii < lim; ++ii) token(ii);
+  for (int k = 0; k < K; ++k) {                        // new entry k is the input at portion index len - K + k
+    const int src = len - K + k;
+    rg_store<V>(st + (size_t)k * width, src >= 0 ? input(src) : rg_load<V>(st + (size_t)(k + len) * width));
   }
 }
 
@@ -80,17 +111,22 @@ IFB_EXPORT int ifb_rglru_conv(const float* proj, long long ld, int x_col, const 
   if (n <= 0) return IFB_OK;
   if (width < 1 || blocks < 1 || width % blocks || taps < 1 || seg < n || x_col < 0 || x_col + width > ld) return IFB_ERR_SIZE;
   if (tile_block != nullptr && (tile < 1 || seg % tile)) return IFB_ERR_SIZE;
-  if (ub_dtype == IFB_BF16)
-    return ifb_launch(rglru_conv_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, proj, ld, x_col, x_bias, conv_w, conv_b,
-                      state, state_slots, cu_q, seq_lens, req_index, u, (__nv_bfloat16*)ub, seg, blocks, offsets, tile_block,
-                      tile, width, taps);
+  const bool vec = (width / blocks) % 4 == 0 && ld % 4 == 0 && x_col % 4 == 0 &&
+                   (((uintptr_t)proj | (uintptr_t)x_bias | (uintptr_t)conv_b | (uintptr_t)state | (uintptr_t)u | (uintptr_t)ub) & 15) == 0;
+#define RC_LAUNCH(TB, V)                                                                                                          \
+  return ifb_launch(rglru_conv_kernel<TB, V>, dim3(n, (width + 128 * V - 1) / (128 * V)), dim3(128), 0, stream, proj, ld, x_col,  \
+                    x_bias, conv_w, conv_b, state, state_slots, cu_q, seq_lens, req_index, u, (TB*)ub, seg, blocks, offsets,      \
+                    tile_block, tile, width, taps)
+  if (ub_dtype == IFB_BF16) { if (vec) RC_LAUNCH(__nv_bfloat16, 4); RC_LAUNCH(__nv_bfloat16, 1); }
   if (ub_dtype != IFB_F32) return IFB_ERR_DTYPE;
-  return ifb_launch(rglru_conv_kernel<float>, dim3(n), dim3(128), 0, stream, proj, ld, x_col, x_bias, conv_w, conv_b, state,
-                    state_slots, cu_q, seq_lens, req_index, u, (float*)ub, seg, blocks, offsets, tile_block, tile, width, taps);
+  if (vec) RC_LAUNCH(float, 4);
+  RC_LAUNCH(float, 1);
+#undef RC_LAUNCH
 }
 
 // ------------------------------------------------------------------------------------------ the recurrence
-constexpr int RG_CHUNK = 64;
+constexpr int RG_CHUNK = 32;
+constexpr int RG_AHEAD = 8;        // tokens whose numbers are formed before the chain takes them
 constexpr int RG_THREADS = 128;
 
 struct RgArgs {
@@ -160,26 +196,42 @@ rglru_scan_kernel(RgArgs g, float* __restrict__ state, const int* __restrict__ s
   if (MODE == 1) {
     if (chunk == 0) *aside = *st;
     float A = 1.f, B = 0.f;
-    for (int t = q0 + lo; t < q0 + hi; ++t) {
-      float a, in;
-      rg_token(g, t, e, b, c, sp, a, in);
-      A *= a;
-      B = fmaf(a, B, in);
+    for (int t = q0 + lo; t < q0 + hi; t += RG_AHEAD) {
+      float a[RG_AHEAD], in[RG_AHEAD];
+#pragma unroll
+      for (int j = 0; j < RG_AHEAD; ++j) {
+        a[j] = 1.f; in[j] = 0.f;
+        if (t + j < q0 + hi) rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < RG_AHEAD; ++j) { A *= a[j]; B = fmaf(a[j], B, in[j]); }
     }
     maps[((size_t)(first_chunk + chunk) * 2) * g.width + e] = A;
     maps[((size_t)(first_chunk + chunk) * 2 + 1) * g.width + e] = B;
     return;
   }
   float S = MODE == 0 ? *st : *aside;
-  if (MODE == 2)
+  if (MODE == 2) {
+#pragma unroll 8
     for (int k = 0; k < chunk; ++k)
       S = fmaf(maps[((size_t)(first_chunk + k) * 2) * g.width + e], S, maps[((size_t)(first_chunk + k) * 2 + 1) * g.width + e]);
+  }
   const float yb = g.y_bias[e];
-  for (int t = q0 + lo; t < q0 + hi; ++t) {
-    float a, in;
-    rg_token(g, t, e, b, c, sp, a, in);
-    S = fmaf(a, S, in);
-    out[(size_t)t * g.width + e] = from_f32<TO>(S * rg_gelu_tanh(g.proj[(size_t)t * g.ld + g.y_col + e] + yb));
+  for (int t = q0 + lo; t < q0 + hi; t += RG_AHEAD) {
+    float a[RG_AHEAD], in[RG_AHEAD], y[RG_AHEAD];
+#pragma unroll
+    for (int j = 0; j < RG_AHEAD; ++j) {
+      a[j] = 1.f; in[j] = 0.f; y[j] = 0.f;
+      if (t + j < q0 + hi) {
+        rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
+        y[j] = rg_gelu_tanh(g.proj[(size_t)(t + j) * g.ld + g.y_col + e] + yb);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RG_AHEAD; ++j) {
+      S = fmaf(a[j], S, in[j]);
+      if (t + j < q0 + hi) out[(size_t)(t + j) * g.width + e] = from_f32<TO>(S * y[j]);
+    }
   }
   if (MODE == 0 || hi == len) *st = S;
 }
