@@ -1064,7 +1064,8 @@ def time_hybrid_kernels(args):
 
 def time_recurrent_kernels(args):
     """The real-gated recurrence's kernels each alone (its convolution, the block-diagonal gate product, the walk), beside
-    the element-wise recurrence of the closest design (minGRU) at the same width: a 2,048-token prompt in one step and a
+    the element-wise recurrence of the closest design (minGRU) and the framework's other short convolution (the one in
+    front of Filorax's sublayers, bfloat16 in and out) at the same width: a 2,048-token prompt in one step and a
     decode step of 8 requests, CUDA events over 20 repetitions, against the bytes each has to move at the least over the
     measured copy bandwidth; one JSON line.  (Also the small case for a profiler.)"""
     import torch
@@ -1129,6 +1130,8 @@ def time_recurrent_kernels(args):
             r["gate_product_" + label] = entry(timed(f), tf=2.0 * n * B * 2 * bs * bs, by=n * W * (2 + 8) + wg.numel() * 2)
             r["recurrence_" + label] = entry(timed(lambda: K.rglru_scan(gates.view(B, seg, 2 * bs), ab, ib, lam, 8.0, u, proj, 0, yb, state,
                                                                         slots, cu, seq, o, max_q_len=max(lens))), by=n * W * 18)
+            h16, cw16, o16 = rnd(n, W, dtype=torch.bfloat16), rnd(W, taps, dtype=torch.bfloat16), torch.zeros(n, W, dtype=torch.bfloat16, device="cuda")
+            r["input_convolution_" + label] = entry(timed(lambda: K.causal_conv(h16, cw16, cstate, slots, cu, seq, req, o16)), by=n * W * 4)
             proj3, ustate = rnd(n, 3 * W), torch.zeros(8, W, device="cuda")
             r["gated_unit_" + label] = entry(timed(lambda: K.gated_unit_scan(proj3, zb, xb2, ustate, slots, cu, seq, o, max_q_len=max(lens))),
                                              by=n * W * 14)

@@ -11,13 +11,15 @@
 // S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu_tanh(y_raw + y_bias).  A thread owns a (request, channel) and walks the
 // request's tokens of the step from the slot's state, eight tokens' numbers formed ahead of the chain.  Long portions are
 // cut into chunks of 32 tokens that run side by side in two launches: the first forms every chunk's map S -> A S + B from zero and sets the slot's state aside, the
-// second folds the maps of the chunks before its own onto that state, walks its chunk and writes the outputs (the last
+// second folds the maps of the chunks before its own onto that state, walks its chunk over the decays and input terms that
+// the first left in the gates' place, and writes the outputs (the last
 // chunk of a request writes the state).  The two forms differ by rounding only.  Everything here is float32 arithmetic.
 #include "common.cuh"
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------ the convolution
-// A block is (token, slice of 128 * V channels); a thread owns V neighbouring channels (V = 4 where widths and addresses
+// A block is (eight tokens, or one in a small step; slice of 128 * V channels) and takes its tokens one after another; a thread
+// owns V neighbouring channels (V = 4 where widths and addresses
 // allow 16-byte accesses, else 1).
 template <int V> struct RgVec { float v[V]; };
 template <int V> __device__ __forceinline__ RgVec<V> rg_load(const float* p) {
@@ -37,17 +39,17 @@ template <int V> __device__ __forceinline__ void rg_store(__nv_bfloat16* p, cons
   } else *p = __float2bfloat16(r.v[0]);
 }
 
+constexpr int RC_TOKENS = 8;        // tokens a block of a large step walks: the start of a block costs a chain of small loads
 template <typename TB, int V>
 __global__ void __launch_bounds__(128)
 rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const float* __restrict__ x_bias,
                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, float* __restrict__ state,
                   const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                   const int* __restrict__ req_index, float* __restrict__ u, TB* __restrict__ ub, int seg, int blocks,
-                  int* __restrict__ offsets, int* __restrict__ tile_block, int tile, int width, int taps) {
+                  int* __restrict__ offsets, int* __restrict__ tile_block, int tile, int width, int taps, int tokens, int per_block) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  const int t = blockIdx.x;
-  if (t == 0 && blockIdx.y == 0) {
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
     for (int b = threadIdx.x; b <= blocks; b += blockDim.x) offsets[b] = b * seg;
     if (tile_block != nullptr) {
       const int per = seg / tile;
@@ -57,6 +59,9 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
   const int e = (blockIdx.y * blockDim.x + threadIdx.x) * V;      // this thread's first channel
   if (e >= width) return;
   const int bs = width / blocks;
+  const RgVec<V> xb = rg_load<V>(x_bias + e), cb = rg_load<V>(conv_b + e);
+  const int t_end = min(tokens, ((int)blockIdx.x + 1) * per_block);
+  for (int t = blockIdx.x * per_block; t < t_end; ++t) {
   const int r = req_index[t];
   const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
   TB* ub_e = ub + ((size_t)(e / bs) * seg) * bs + e % bs;          // + row * bs: the V channels lie in one block (bs % V == 0)
@@ -66,13 +71,12 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
     for (int v = 0; v < V; ++v) z.v[v] = 0.f;
     rg_store<V>(u + (size_t)t * width + e, z);
     rg_store<V>(ub_e + (size_t)t * bs, z);
-    return;
+    continue;
   }
   const int K = taps - 1, Kp = K > 0 ? K : 1;
-  if (i > 0 && i < K) return;                          // the block of the portion's first token computes these
+  if (i > 0 && i < K) continue;                        // the thread that has the portion's first token computes these
   float* st = state + (size_t)state_slots[r] * Kp * width + e;
   const float* xr = proj + x_col + e;
-  const RgVec<V> xb = rg_load<V>(x_bias + e), cb = rg_load<V>(conv_b + e);
   // input idx of the portion (negative: from the state)
   auto input = [&](int idx) -> RgVec<V> {
     if (idx < 0) return rg_load<V>(st + (size_t)(K + idx) * width);
@@ -93,7 +97,7 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
   };
   if (i >= K) {                                        // reads this step's rows only
     token(i);
-    return;
+    continue;
   }
   // i == 0 and K > 0: the tokens that read the state, then the state's replacement; a channel is one thread's throughout
   const int lim = len < K ? len : K;
@@ -101,6 +105,7 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
   for (int k = 0; k < K; ++k) {                        // new entry k is the input at portion index len - K + k
     const int src = len - K + k;
     rg_store<V>(st + (size_t)k * width, src >= 0 ? input(src) : rg_load<V>(st + (size_t)(k + len) * width));
+  }
   }
 }
 
@@ -114,9 +119,13 @@ IFB_EXPORT int ifb_rglru_conv(const float* proj, long long ld, int x_col, const 
   const bool vec = (width / blocks) % 4 == 0 && ld % 4 == 0 && x_col % 4 == 0 &&
                    (((uintptr_t)proj | (uintptr_t)x_bias | (uintptr_t)conv_b | (uintptr_t)state | (uintptr_t)u | (uintptr_t)ub) & 15) == 0;
 #define RC_LAUNCH(TB, V)                                                                                                          \
-  return ifb_launch(rglru_conv_kernel<TB, V>, dim3(n, (width + 128 * V - 1) / (128 * V)), dim3(128), 0, stream, proj, ld, x_col,  \
-                    x_bias, conv_w, conv_b, state, state_slots, cu_q, seq_lens, req_index, u, (TB*)ub, seg, blocks, offsets,      \
-                    tile_block, tile, width, taps)
+  {                                                                                                                               \
+    const int ys = (width + 128 * V - 1) / (128 * V);                                                                             \
+    const int per = (long long)n * ys >= 4096 ? RC_TOKENS : 1;          /* a small step keeps a block per token */                \
+    return ifb_launch(rglru_conv_kernel<TB, V>, dim3((n + per - 1) / per, ys), dim3(128), 0, stream, proj, ld, x_col, x_bias,      \
+                      conv_w, conv_b, state, state_slots, cu_q, seq_lens, req_index, u, (TB*)ub, seg, blocks, offsets, tile_block, \
+                      tile, width, taps, n, per);                                                                                 \
+  }
   if (ub_dtype == IFB_BF16) { if (vec) RC_LAUNCH(__nv_bfloat16, 4); RC_LAUNCH(__nv_bfloat16, 1); }
   if (ub_dtype != IFB_F32) return IFB_ERR_DTYPE;
   if (vec) RC_LAUNCH(float, 4);
@@ -130,7 +139,7 @@ constexpr int RG_AHEAD = 8;        // tokens whose numbers are formed before the
 constexpr int RG_THREADS = 128;
 
 struct RgArgs {
-  const float* gates; int seg, bs;         // [blocks * seg, 2 bs]: row b * seg + t holds r | i of block b
+  float* gates; int seg, bs;               // [blocks * seg, 2 bs]: row b * seg + t holds r | i of block b
   const float* a_bias; const float* i_bias; const float* lam; float scale;
   const float* u;                          // [n, width]
   const float* proj; long long ld; int y_col; const float* y_bias;
@@ -154,7 +163,8 @@ __device__ __forceinline__ void rg_token(const RgArgs& g, int t, int e, int b, i
 }
 
 // MODE 0: a thread walks all tokens of (request, channel) from the slot's state and writes it back.
-// MODE 1: a thread forms the map of (chunk, channel) from zero; chunk 0 of a request sets the slot's state aside.
+// MODE 1: a thread forms the map of (chunk, channel) from zero and leaves every token's decay and input term where its raw
+//         gates were (each is read and written by this thread only); chunk 0 of a request sets the slot's state aside.
 // MODE 2: a thread folds the earlier chunks' maps onto the state set aside, walks its chunk, writes outputs (and the state
 //         after the request's last chunk).
 // scratch: [requests][width] states set aside, then [chunk slots][2][width] maps; chunk slots are numbered request by
@@ -204,7 +214,13 @@ rglru_scan_kernel(RgArgs g, float* __restrict__ state, const int* __restrict__ s
         if (t + j < q0 + hi) rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
       }
 #pragma unroll
-      for (int j = 0; j < RG_AHEAD; ++j) { A *= a[j]; B = fmaf(a[j], B, in[j]); }
+      for (int j = 0; j < RG_AHEAD; ++j) {
+        A *= a[j]; B = fmaf(a[j], B, in[j]);
+        if (t + j < q0 + hi) {               // the second launch reads the decay and the input term where the raw gates were
+          float* row = g.gates + ((size_t)b * g.seg + t + j) * (2 * g.bs);
+          row[c] = a[j]; row[g.bs + c] = in[j];
+        }
+      }
     }
     maps[((size_t)(first_chunk + chunk) * 2) * g.width + e] = A;
     maps[((size_t)(first_chunk + chunk) * 2 + 1) * g.width + e] = B;
@@ -223,7 +239,12 @@ rglru_scan_kernel(RgArgs g, float* __restrict__ state, const int* __restrict__ s
     for (int j = 0; j < RG_AHEAD; ++j) {
       a[j] = 1.f; in[j] = 0.f; y[j] = 0.f;
       if (t + j < q0 + hi) {
-        rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
+        if (MODE == 2) {
+          const float* row = g.gates + ((size_t)b * g.seg + t + j) * (2 * g.bs);
+          a[j] = row[c]; in[j] = row[g.bs + c];
+        } else {
+          rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
+        }
         y[j] = rg_gelu_tanh(g.proj[(size_t)(t + j) * g.ld + g.y_col + e] + yb);
       }
     }
@@ -257,7 +278,7 @@ static int rg_launch(const RgArgs& g, float* state, const int* state_slots, cons
 }
 
 // scratch null: the one-launch walk; else the chunked form (ifb_rglru_scratch_floats floats)
-IFB_EXPORT int ifb_rglru_scan(const float* gates, int seg, int blocks, const float* a_bias, const float* i_bias, const float* lam,
+IFB_EXPORT int ifb_rglru_scan(float* gates, int seg, int blocks, const float* a_bias, const float* i_bias, const float* lam,
                               float scale, const float* u, const float* proj, long long ld, int y_col, const float* y_bias,
                               float* state, const int* state_slots, const int* cu_q, const int* seq_lens, void* out, int out_dtype,
                               float* scratch, int requests, int n, int width, cudaStream_t stream) {

@@ -1098,7 +1098,8 @@ class CudaKernels:
         [blocks, seg, 2 bs] float32: the block-diagonal products' raw r | i; r = sigmoid(. + a_bias), i = sigmoid(. + i_bias),
         log a = -decay_scale * r * softplus(decay), S <- a S + sqrt(1 - a^2) * i * u on state [slots, width] float32;
         out = S * gelu_tanh(proj[:, y_col : y_col + width] + y_bias).  From ``scan_block_min`` tokens on the requests are
-        cut into chunks of 32 tokens that run side by side (two launches), which differs by rounding only."""
+        cut into chunks of 32 tokens that run side by side (two launches), which differs by rounding only; that form leaves
+        the decays and input terms in ``gates``."""
         _dense(gates, "gates", torch.float32), _dense(u, "u", torch.float32), _dense(proj, "proj", torch.float32)
         _dense(state, "state", torch.float32), _dense(out, "out")
         for t, name in ((a_bias, "a_bias"), (i_bias, "i_bias"), (decay, "decay"), (y_bias, "y_bias")):
