@@ -9,11 +9,11 @@
 // (2) rglru_scan: per channel of a float32 state, r = sigmoid(gr + a_bias), i = sigmoid(gi + i_bias) from the gate products'
 // float32 results (block-major rows of [r | i]), log a = -scale * r * softplus(lam), a = exp(log a),
 // S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu_tanh(y_raw + y_bias).  A thread owns a (request, channel) and walks the
-// request's tokens of the step from the slot's state, eight tokens' numbers formed ahead of the chain.  Long portions are
-// cut into chunks of 32 tokens that run side by side in two launches: the first forms every chunk's map S -> A S + B from zero and sets the slot's state aside, the
-// second folds the maps of the chunks before its own onto that state, walks its chunk over the decays and input terms that
-// the first left in the gates' place, and writes the outputs (the last
-// chunk of a request writes the state).  The two forms differ by rounding only.  Everything here is float32 arithmetic.
+// request's tokens of the step from the slot's state, eight tokens' numbers formed ahead of the chain.  Long portions run
+// in three launches: every (token, channel) pair's decay and input term side by side, left where the pair's raw gates were;
+// then, over chunks of 32 tokens side by side, every chunk's map S -> A S + B from zero (the slot's state is set aside);
+// then each chunk folds the maps of the chunks before its own onto that state, walks its tokens and writes the outputs (the
+// last chunk of a request writes the state).  The two forms differ by rounding only.  Everything here is float32 arithmetic.
 #include "common.cuh"
 #include <math.h>
 
@@ -162,9 +162,33 @@ __device__ __forceinline__ void rg_token(const RgArgs& g, int t, int e, int b, i
   in = sqrtf(fmaxf(-expm1f(2.f * loga), 0.f)) * i * g.u[(size_t)t * g.width + e];
 }
 
+// The chunked form's first launch: every (token, channel) pair's decay and input term, side by side, left where the pair's
+// raw gates were (each pair is one thread's).
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_terms_kernel(RgArgs g, int tokens) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int e = blockIdx.x * RG_THREADS + threadIdx.x;
+  if (e >= g.width) return;
+  const int b = e / g.bs, c = e - b * g.bs;
+  const float sp = rg_softplus(g.lam[e]);
+  const int t0 = blockIdx.y * RG_AHEAD;
+  float a[RG_AHEAD], in[RG_AHEAD];
+#pragma unroll
+  for (int j = 0; j < RG_AHEAD; ++j)
+    if (t0 + j < tokens) rg_token(g, t0 + j, e, b, c, sp, a[j], in[j]);
+#pragma unroll
+  for (int j = 0; j < RG_AHEAD; ++j)
+    if (t0 + j < tokens) {
+      float* row = g.gates + ((size_t)b * g.seg + t0 + j) * (2 * g.bs);
+      row[c] = a[j];
+      row[g.bs + c] = in[j];
+    }
+}
+
 // MODE 0: a thread walks all tokens of (request, channel) from the slot's state and writes it back.
-// MODE 1: a thread forms the map of (chunk, channel) from zero and leaves every token's decay and input term where its raw
-//         gates were (each is read and written by this thread only); chunk 0 of a request sets the slot's state aside.
+// MODE 1: a thread forms the map of (chunk, channel) from zero out of the decays and input terms that rglru_terms_kernel
+//         left in the gates' place; chunk 0 of a request sets the slot's state aside.
 // MODE 2: a thread folds the earlier chunks' maps onto the state set aside, walks its chunk, writes outputs (and the state
 //         after the request's last chunk).
 // scratch: [requests][width] states set aside, then [chunk slots][2][width] maps; chunk slots are numbered request by
@@ -211,16 +235,13 @@ rglru_scan_kernel(RgArgs g, float* __restrict__ state, const int* __restrict__ s
 #pragma unroll
       for (int j = 0; j < RG_AHEAD; ++j) {
         a[j] = 1.f; in[j] = 0.f;
-        if (t + j < q0 + hi) rg_token(g, t + j, e, b, c, sp, a[j], in[j]);
-      }
-#pragma unroll
-      for (int j = 0; j < RG_AHEAD; ++j) {
-        A *= a[j]; B = fmaf(a[j], B, in[j]);
-        if (t + j < q0 + hi) {               // the second launch reads the decay and the input term where the raw gates were
-          float* row = g.gates + ((size_t)b * g.seg + t + j) * (2 * g.bs);
-          row[c] = a[j]; row[g.bs + c] = in[j];
+        if (t + j < q0 + hi) {
+          const float* row = g.gates + ((size_t)b * g.seg + t + j) * (2 * g.bs);
+          a[j] = row[c]; in[j] = row[g.bs + c];
         }
       }
+#pragma unroll
+      for (int j = 0; j < RG_AHEAD; ++j) { A *= a[j]; B = fmaf(a[j], B, in[j]); }
     }
     maps[((size_t)(first_chunk + chunk) * 2) * g.width + e] = A;
     maps[((size_t)(first_chunk + chunk) * 2 + 1) * g.width + e] = B;
@@ -270,7 +291,9 @@ static int rg_launch(const RgArgs& g, float* state, const int* state_slots, cons
     return ifb_launch(rglru_scan_kernel<TO, 0>, dim3(requests, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q,
                       seq_lens, out, scratch, requests);
   const unsigned chunks = (unsigned)((n + RG_CHUNK - 1) / RG_CHUNK + requests);
-  const int rc = ifb_launch(rglru_scan_kernel<TO, 1>, dim3(chunks, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q,
+  int rc = ifb_launch(rglru_terms_kernel, dim3(ey, (unsigned)((n + RG_AHEAD - 1) / RG_AHEAD)), dim3(RG_THREADS), 0, stream, g, n);
+  if (rc != IFB_OK) return rc;
+  rc = ifb_launch(rglru_scan_kernel<TO, 1>, dim3(chunks, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q,
                             seq_lens, out, scratch, requests);
   if (rc != IFB_OK) return rc;
   return ifb_launch(rglru_scan_kernel<TO, 2>, dim3(chunks, ey), dim3(RG_THREADS), 0, stream, g, state, state_slots, cu_q, seq_lens,

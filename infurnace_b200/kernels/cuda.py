@@ -1098,8 +1098,8 @@ class CudaKernels:
         [blocks, seg, 2 bs] float32: the block-diagonal products' raw r | i; r = sigmoid(. + a_bias), i = sigmoid(. + i_bias),
         log a = -decay_scale * r * softplus(decay), S <- a S + sqrt(1 - a^2) * i * u on state [slots, width] float32;
         out = S * gelu_tanh(proj[:, y_col : y_col + width] + y_bias).  From ``scan_block_min`` tokens on the requests are
-        cut into chunks of 32 tokens that run side by side (two launches), which differs by rounding only; that form leaves
-        the decays and input terms in ``gates``."""
+        run in three launches (the gates' arithmetic side by side for every token, then chunks of 32 tokens side by side
+        twice), which differs by rounding only; that form leaves the decays and input terms in ``gates``."""
         _dense(gates, "gates", torch.float32), _dense(u, "u", torch.float32), _dense(proj, "proj", torch.float32)
         _dense(state, "state", torch.float32), _dense(out, "out")
         for t, name in ((a_bias, "a_bias"), (i_bias, "i_bias"), (decay, "decay"), (y_bias, "y_bias")):
@@ -1119,7 +1119,7 @@ class CudaKernels:
                 self.scratch_generation += 1
             scratch = self._rg_scratch.data_ptr()
             self.rglru_chunked_calls += 1
-        self.launches += 2 if scratch else 1
+        self.launches += 3 if scratch else 1
         _check(lib.ifb_rglru_scan(gates.data_ptr(), seg, blocks, a_bias.data_ptr(), i_bias.data_ptr(), decay.data_ptr(),
                                   float(decay_scale), u.data_ptr(), proj.data_ptr(), proj.shape[1], int(y_col), y_bias.data_ptr(),
                                   state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
