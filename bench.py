@@ -680,7 +680,7 @@ def recurrent_config(size):
         elif i % 4 == 2:
             entries.append({"type": "attention", "mlp": mlp, "mixer": {
                 "heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": window},
-                "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}})
+                "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}})
         else:
             entries.append({"type": "rglru", "mlp": mlp, "mixer": {"width": W, "blocks": W // 128, "conv": 4}})
     return {"architecture": "Golonex", "layers": entries, "norm": {"eps": 1e-6}, "vocab": 32768, "width": W,

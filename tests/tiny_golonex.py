@@ -69,12 +69,12 @@ TINY = {
         _att(4, 1, 4, 0.7, None, 30.0, 2, None),
         _lat(2, 4, 8, 4, 8, 16, 0.4, None, 500.0, _moe(2, 2, 8))]),
                page_size=8, store="bfloat16", seed=32),
-    # wider, sizes the tensor-core routes take: heads of 64 and 32, latents of 64 and 96, windows of 33 and 50
-    "G3": dict(config=_config(331, 256, 1e-5, [
-        _lat(4, 32, 32, 64, 64, 96, 0.2, 33, 10000.0, _moe(8, 2, 64, shared=128)),
-        _rec(192, 4, 4, _moe(4, 3, 128, shared=64)),
-        _att(8, 2, 64, 0.12, 50, 10000.0, 32, _moe(8, 1, 32), scaling=(2.0, 256, 16.0, 1.0)),
-        _lat(8, 16, 16, 16, 96, 48, 0.3, 120, 20000.0, None)], cap=12.0, side=16),
+    # wider, sizes the tensor-core routes take: heads of 48 and 24, latents of 72 and 96, windows of 33, 50 and 120
+    "G3": dict(config=_config(331, 320, 1e-6, [
+        _lat(5, 24, 16, 48, 72, 88, 0.2, 33, 10000.0, _moe(6, 2, 40, shared=96)),
+        _rec(224, 4, 3, _moe(4, 3, 128, shared=64)),
+        _att(6, 3, 48, 0.14, 50, 10000.0, 16, _moe(7, 1, 24), scaling=(3.0, 200, 12.0, 1.5)),
+        _lat(8, 16, 16, 16, 96, 48, 0.3, 120, 5000.0, None)], cap=10.0, side=12),
                page_size=16, store="bfloat16", seed=33, sharpen=2.0),       # run in bfloat16 over hundreds of tokens
 }
 
