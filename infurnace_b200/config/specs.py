@@ -594,7 +594,9 @@ class RotaryValueAttentionSpec:
     mean square (no weight) before it is cached.  ``value_position``: the value of position j is rotated by j over
     that description's width before it is cached, and each head's summed output at position i is rotated back by
     -i.  Causal, optional window, plain softmax; key and value heads may differ in width.  ``v_proj`` None: the
-    values are the keys as projected, before their rotation, and the model has no v matrix."""
+    values are the keys as projected, before their rotation, and the model has no v matrix.  ``weight_terms``: on the
+    tensor-core routes a softmax weight, formed in float32, enters the weighted sum as one bfloat16 number or as two
+    (its rounding and what the rounding left out: 16 bits of the float32 weight, two products)."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -610,6 +612,7 @@ class RotaryValueAttentionSpec:
     value_norm: bool = False
     value_position: Optional[RotarySpec] = None
     window: Optional[int] = None
+    weight_terms: int = 1
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         W = self.hidden_size
@@ -776,7 +779,8 @@ class LatentAttentionSpec:
     of it joins the softmax's denominator, with no key and no value.  ``gate``: the heads side by side are multiplied by
     sigmoid(G h) before ``o_proj``; with ``gate_per_head`` G has one row per head and the whole head takes one number.
     ``q_rank`` r: the queries go through a latent of their own, q = ``q_proj`` (rmsnorm(``q_down`` h) * ``q_norm``),
-    with ``q_down`` [r, hidden], ``q_norm`` [r] and ``q_proj`` [heads * (head_dim + rot_dim), r]."""
+    with ``q_down`` [r, hidden], ``q_norm`` [r] and ``q_proj`` [heads * (head_dim + rot_dim), r].  ``weight_terms``: as
+    :class:`RotaryValueAttentionSpec`'s."""
     hidden_size: int
     num_heads: int
     head_dim: int
@@ -799,6 +803,7 @@ class LatentAttentionSpec:
     q_rank: Optional[int] = None
     q_down: Optional[str] = None
     q_norm: Optional[str] = None
+    weight_terms: int = 1
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         W, H = self.hidden_size, self.num_heads

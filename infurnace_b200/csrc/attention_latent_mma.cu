@@ -40,6 +40,11 @@ __device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// what the rounding of (lo, hi) to bfloat16 left out, itself rounded to bfloat16: the second term of a two-term weight
+__device__ __forceinline__ uint32_t lm_pack_rest(float lo, float hi) {
+  const float2 f = __bfloat1622float2(__floats2bfloat162_rn(lo, hi));
+  return lm_pack(lo - f.x, hi - f.y);
+}
 // 2^x of a weight that is rounded to bfloat16 next: the approximation's error is far below that rounding
 __device__ __forceinline__ float lm_ex2(float x) {
   float y;
@@ -60,7 +65,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
                             const bf16* __restrict__ rot_pages, const int* __restrict__ block_tables, int table_stride, int page_size,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_lens, const void* __restrict__ sink, int stype,
                             bf16* __restrict__ out, float* __restrict__ part, int heads, int rank, int rot, int rot_pad,
-                            float scale, int window, int splits) {
+                            float scale, int window, int splits, int terms) {
   extern __shared__ __align__(16) unsigned char lm_raw[];
   if (ROTP >= 0) rot_pad = ROTP;
   const int KD = RANK + rot_pad, LD = KD + 8;      // columns of a row, and its length in shared memory
@@ -226,12 +231,22 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
       for (int ks = 0; ks < LM_KEYS / 16; ++ks) {
         uint32_t a[4] = {lm_pack(s[2 * ks][0], s[2 * ks][1]), lm_pack(s[2 * ks][2], s[2 * ks][3]),
                          lm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), lm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+        // terms == 2: a weight is the sum of two bfloat16 numbers (16 bits of its float32 value) and the sum takes two products
+        uint32_t a2[4] = {0u, 0u, 0u, 0u};
+        if (terms == 2) {
+          a2[0] = lm_pack_rest(s[2 * ks][0], s[2 * ks][1]); a2[1] = lm_pack_rest(s[2 * ks][2], s[2 * ks][3]);
+          a2[2] = lm_pack_rest(s[2 * ks + 1][0], s[2 * ks + 1][1]); a2[3] = lm_pack_rest(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+        }
 #pragma unroll
         for (int np = 0; np < RANK / 16; ++np) {
           uint32_t b[4];
           lm_ldm_t(b, Kt + (size_t)(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + np * 16 + (lane >> 4) * 8);
           lm_mma(o[2 * np], a, b[0], b[1]);
           lm_mma(o[2 * np + 1], a, b[2], b[3]);
+          if (terms == 2) {
+            lm_mma(o[2 * np], a2, b[0], b[1]);
+            lm_mma(o[2 * np + 1], a2, b[2], b[3]);
+          }
         }
       }
     }
@@ -320,7 +335,7 @@ template <int RANK, int ROTP>
 static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void* lat_pages, const void* rot_pages, const int* block_tables,
                      int table_stride, int page_size, const int* cu_q, const int* seq_lens, const void* sink, int stype, void* out,
                      float* part, int requests, int max_q_len, int heads, int rank, int rot, float scale, int window, int splits,
-                     cudaStream_t stream) {
+                     int terms, cudaStream_t stream) {
   const int rot_pad = (rot + 15) / 16 * 16, LD = RANK + rot_pad + 8;
   const size_t smem = (size_t)(LM_ROWS + 2 * LM_KEYS) * LD * sizeof(bf16);
   if (smem > 220 * 1024) return IFB_ERR_SIZE;
@@ -328,7 +343,7 @@ static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void
   const dim3 grid((unsigned)(((long long)max_q_len * heads + LM_ROWS - 1) / LM_ROWS), (unsigned)requests, (unsigned)splits);
   int rc = ifb_launch(latent_attention_mma_kernel<RANK, ROTP>, grid, dim3(LM_THREADS), smem, stream, q_lat, q_rot, seg, (const bf16*)lat_pages,
                       (const bf16*)rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, (bf16*)out, part, heads,
-                      rank, rot, rot_pad, scale, window, splits);
+                      rank, rot, rot_pad, scale, window, splits, terms);
   if (rc != IFB_OK || splits <= 1) return rc;
   return ifb_launch(latent_attention_merge_kernel<RANK>, dim3((unsigned)(max_q_len * heads), grid.y), dim3(LM_THREADS), 0, stream,
                     (const float*)part, cu_q, seq_lens, sink, stype, (bf16*)out, seg, heads, rank, splits, (int)grid.x);
@@ -338,14 +353,15 @@ static int lm_launch(const float* q_lat, const float* q_rot, int seg, const void
 IFB_EXPORT int ifb_latent_attention_mma(const float* q_lat, const float* q_rot, int seg, const void* lat_pages, const void* rot_pages,
                                         const int* block_tables, int table_stride, int page_size, const int* cu_q, const int* seq_lens,
                                         const void* sink, int stype, void* out, float* part, int requests, int max_q_len, int heads,
-                                        int rank, int rot, float scale, int window, int splits, cudaStream_t stream) {
+                                        int rank, int rot, float scale, int window, int splits, int terms, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return IFB_OK;
+  if (terms != 1 && terms != 2) return IFB_ERR_ARG;
   if (heads < 1 || rank < 8 || rank > 256 || rank % 8 || rot < 0 || rot % 8 || page_size < 1 || window < 0 || splits < 1 || splits > 32 ||
       (splits > 1 && part == nullptr) || (((uintptr_t)q_lat | (uintptr_t)q_rot) & 15))      // queries are read 16 bytes at a time
     return IFB_ERR_SIZE;
 #define LM_ARGS                                                                                                                \
   q_lat, q_rot, seg, lat_pages, rot_pages, block_tables, table_stride, page_size, cu_q, seq_lens, sink, stype, out, part, requests, \
-      max_q_len, heads, rank, rot, scale, window, splits, stream
+      max_q_len, heads, rank, rot, scale, window, splits, terms, stream
   // the usual widths of a rotated part have kernels of their own; any other width runs the one that reads it at run time
 #define LM_CASE(P)                                            \
   switch ((rot + 15) / 16 * 16) {                             \

@@ -77,6 +77,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// WEIGHT_TERMS 2 (a library variant of its own): a softmax weight enters the P V product as the sum of two bfloat16 numbers,
+// its rounding and what the rounding left out (16 bits of the float32 weight), and the product takes two instructions.
+#ifndef WEIGHT_TERMS
+#define WEIGHT_TERMS 1
+#endif
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi);
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi) {
+  const float2 f = __bfloat1622float2(__floats2bfloat162_rn(lo, hi));
+  return pack_bf16(lo - f.x, hi - f.y);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -241,6 +251,13 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
     a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
     a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
     a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#if WEIGHT_TERMS == 2
+    uint32_t a2[4];
+    a2[0] = pack_bf16_rest(s[2 * kk][0], s[2 * kk][1]);
+    a2[1] = pack_bf16_rest(s[2 * kk][2], s[2 * kk][3]);
+    a2[2] = pack_bf16_rest(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a2[3] = pack_bf16_rest(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#endif
 #pragma unroll
     for (int n2 = 0; n2 < KB; ++n2) {
       uint32_t b[4];
@@ -249,6 +266,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KB][4], const bf1
       ldmatrix_x4_trans(b, kv_at<SWZ>(Vs, key, col));
       mma_bf16(o[2 * n2], a, b[0], b[1]);
       mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+#if WEIGHT_TERMS == 2
+      mma_bf16(o[2 * n2], a2, b[0], b[1]);
+      mma_bf16(o[2 * n2 + 1], a2, b[2], b[3]);
+#endif
     }
   }
 }

@@ -552,7 +552,10 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ attention
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
-                        scale, window, max_q_len, max_seq_len, min_q_len=1):
+                        scale, window, max_q_len, max_seq_len, min_q_len=1, weight_terms=1):
+        """``weight_terms`` 2 (tensor-core route only): a softmax weight enters the weighted sum as two bfloat16 terms, its
+        rounding and what the rounding left out, so that 16 bits of the float32 weight count; the tcgen05 prompt kernel, which
+        has one term, is then not taken."""
         _dense(qkv, "qkv"), _dense(kv_pages, "kv_pages", qkv.dtype), _dense(out, "out", qkv.dtype)
         _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
         if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
@@ -569,7 +572,7 @@ class CudaKernels:
                 and num_heads % num_kv_heads == 0:
             return self._paged_attention_mma(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q,
                                              seq_lens, out, scale, window, max_q_len, max_seq_len, n, r,
-                                             min_q_len=min_q_len)
+                                             min_q_len=min_q_len, weight_terms=weight_terms)
         self.launches += 1
         _check(self.core.ifb_paged_attention_simt(
             qkv.data_ptr(), _code(qkv), qkv.stride(0), kv_pages.data_ptr(), block_tables.data_ptr(),
@@ -592,16 +595,20 @@ class CudaKernels:
             num_heads, num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window), int(max_q_len), self._stream()),
             "paged_attention")
 
-    def attention_library(self, head_dim):
-        lib = self._attn_mma.get(head_dim)
+    def attention_library(self, head_dim, weight_terms=1):
+        if weight_terms not in (1, 2):
+            raise KernelError("attention: a softmax weight has one or two bfloat16 terms")
+        key = head_dim if weight_terms == 1 else (head_dim, weight_terms)
+        lib = self._attn_mma.get(key)
         if lib is None:
-            lib = load_library("attention_mma", {"HEAD_DIM": head_dim}, progress=self._progress)
+            defines = {"HEAD_DIM": head_dim} if weight_terms == 1 else {"HEAD_DIM": head_dim, "WEIGHT_TERMS": weight_terms}
+            lib = load_library("attention_mma", defines, progress=self._progress)
             lib.ifb_attention_mma.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
             lib.ifb_attention_mma_scratch_floats.restype = c_longlong
             lib.ifb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
-            self._attn_mma[head_dim] = lib
+            self._attn_mma[key] = lib
         return lib
 
     def attention_splits(self, num_requests, num_kv_heads, max_seq_len, window=0):
@@ -620,8 +627,8 @@ class CudaKernels:
         return self._attn_scratch
 
     def _paged_attention_mma(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out,
-                             scale, window, max_q_len, max_seq_len, n, r, num_splits=None, min_q_len=1):
-        lib = self.attention_library(head_dim)
+                             scale, window, max_q_len, max_seq_len, n, r, num_splits=None, min_q_len=1, weight_terms=1):
+        lib = self.attention_library(head_dim, weight_terms)
         group = num_heads // num_kv_heads
         only_small = max_q_len * group <= 16
         if num_splits is None:
@@ -636,7 +643,7 @@ class CudaKernels:
                 self._attn_counters = torch.zeros(max(r * num_kv_heads, 4096), dtype=torch.int32, device="cuda")
                 self.scratch_generation += 1
             counters = self._attn_counters
-        use_tc = (not only_small and self.attention_tc and head_dim == 128 and 128 % group == 0
+        use_tc = (not only_small and self.attention_tc and weight_terms == 1 and head_dim == 128 and 128 % group == 0
                   and kv_pages.shape[3] in (16, 32, 64) and kv_pages.data_ptr() % 128 == 0)
         if use_tc:
             self._attention_tc(qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
@@ -1401,7 +1408,7 @@ class CudaKernels:
                                                c_float, c_int, c_void_p]
             m.ifb_latent_attention_mma.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                   c_float, c_int, c_int, c_void_p]
+                                                   c_float, c_int, c_int, c_int, c_void_p]
             m.ifb_latent_attention_mma_scratch_floats.restype = c_longlong
             m.ifb_latent_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         return self._lat
@@ -1497,7 +1504,7 @@ class CudaKernels:
                                                   self._stream()), "latent_prepare")
 
     def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
-                         window, tokens, max_q_len=None, max_seq_len=None, exact=False):
+                         window, tokens, max_q_len=None, max_seq_len=None, exact=False, weight_terms=1):
         """Attention of every head over the request's cached latents (the absorbed form): q_lat [heads, seg, rank] float32,
         q_rot [n, heads, rot] float32 (None without a rotated part), out [heads, seg, rank] = the softmax-weighted sum of
         latents per head.  ``sink`` [heads]: exp of it joins the denominator.  ``window`` 0: every earlier position.
@@ -1505,7 +1512,8 @@ class CudaKernels:
         bfloat16 pages with a latent of at most 256 entries (latent and rotated part multiples of 8), when the caller gives
         the step's longest portion and context: the tensor-core kernel (csrc/attention_latent_mma.cu; float32 scores,
         softmax and sums, the weights rounded to bfloat16 as the left operand of the weighted sum), the context divided
-        among several CTAs where a step has few rows.  float32, other sizes and ``exact``: the plain kernel, a warp per
+        among several CTAs where a step has few rows; ``weight_terms`` 2: a weight enters the sum as two bfloat16 terms, its
+        rounding and what the rounding left out).  float32, other sizes and ``exact``: the plain kernel, a warp per
         (token, head), which keeps float32 weights through the sum."""
         _dense(q_lat, "q_lat", torch.float32), _dense(latent_pages, "latent_pages"), _dense(out, "out", latent_pages.dtype)
         heads, seg, rank = q_lat.shape
@@ -1534,7 +1542,7 @@ class CudaKernels:
                                                 latent_pages.shape[2], cu_q.data_ptr(), seq_lens.data_ptr(), _ptr(sink),
                                                 _code(sink) if sink is not None else 0, out.data_ptr(), _ptr(scratch), requests,
                                                 int(max_q_len), heads, rank, rot, float(scale), int(window or 0), splits,
-                                                self._stream()), "latent_attention")
+                                                int(weight_terms), self._stream()), "latent_attention")
             return
         self.launches += 1
         _check(self._lat_lib().ifb_latent_attention(q_lat.data_ptr(), _ptr(q_rot) if rot else None, seg, latent_pages.data_ptr(),

@@ -27,6 +27,7 @@ MAX_POSITIONS = 1 << 20        # positions have no end in this design; block tab
 EXPERT_ACTIVATION = "silu"
 SIDE_ACTIVATION = "gelu_tanh"
 DECAY_SCALE = 8.0              # log a = -8 * r * softplus(lam)
+WEIGHT_TERMS = 2               # softmax weights are 32-bit in this design: on tensor cores they enter the sum as two bfloat16 terms
 
 
 def _rotary(rot, width):
@@ -52,12 +53,12 @@ def _mixer(kind, m, p, W, eps):
             kv_rank=m["kv_rank"], scale=float(m["scale"]), eps=eps, q_proj=p + "uq", down_proj=p + "dkv",
             latent_norm=p + "dkv.norm", k_up=p + "uk", v_up=p + "uv", o_proj=p + "o",
             position=_rotary(m["rot"], rot_dim) if rot_dim else None, window=_window(m), sink=p + "sink", gate=p + "g",
-            gate_per_head=True, q_rank=m["q_rank"], q_down=p + "dq", q_norm=p + "dq.norm")
+            gate_per_head=True, q_rank=m["q_rank"], q_down=p + "dq", q_norm=p + "dq.norm", weight_terms=WEIGHT_TERMS)
     assert kind == ATTENTION
     return RotaryValueAttentionSpec(
         hidden_size=W, num_heads=m["heads"], num_kv_heads=m["kv_heads"], head_dim=m["dim"], value_head_dim=m["dim"],
         scale=float(m["scale"]), eps=eps, q_proj=p + "q", k_proj=p + "k", v_proj=None, o_proj=p + "o",
-        position=_rotary(m["rot"], m["dim"]) if m.get("rot") else None, window=_window(m))
+        position=_rotary(m["rot"], m["dim"]) if m.get("rot") else None, window=_window(m), weight_terms=WEIGHT_TERMS)
 
 
 def _mlp(mlp, p, W):

@@ -51,6 +51,7 @@ class LatentAttention:
         self.position = build_part(s.position, weights, runtime) if s.position is not None else None
         import os
         self.exact_weights = os.environ.get("INFURNACE_EXACT_ATTENTION", "0") not in ("", "0")
+        self.terms = {"weight_terms": s.weight_terms} if s.weight_terms != 1 else {}
 
     def _segment(self, n):
         """Rows of a head's segment in the grouped products, and the tile of the tcgen05 route (0: the other route)."""
@@ -101,7 +102,7 @@ class LatentAttention:
         o_lat = ctx.buffer("la_o_lat", (H * seg, R), act, rows=H * cap)
         k.latent_attention(q_lat.view(H, seg, R), q_rot, lat_pages, rot_pages, kv.block_tables, ctx.cu_q, ctx.seq_lens, ctx.req_index,
                            self.sink, o_lat.view(H, seg, R), s.scale, s.window or 0, n, max_q_len=ctx.max_q_len,
-                           max_seq_len=ctx.max_seq_len, exact=self.exact_weights)
+                           max_seq_len=ctx.max_seq_len, exact=self.exact_weights, **self.terms)
         y = ctx.buffer("la_y", (H * seg, V), torch.float32, rows=H * cap)
         if tile:
             k.moe_linear_grouped(o_lat, self.w_values, tiles, y)

@@ -70,7 +70,8 @@ class RotaryValueAttention:
         if self._on_tensor_cores(kv):
             # the framework's tensor-core attention over the entry's one tensor of keys and values, then the turn back
             k.paged_attention(q, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables, ctx.cu_q, ctx.seq_lens, out,
-                              s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len, min_q_len=ctx.min_q_len)
+                              s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len, min_q_len=ctx.min_q_len,
+                              **({"weight_terms": s.weight_terms} if s.weight_terms != 1 else {}))
             if v_table is not None:
                 k.rotate_rows(out, v_table, s.num_heads, s.value_head_dim, s.value_head_dim, bool(s.value_position.interleaved),
                               back=True)

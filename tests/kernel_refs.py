@@ -159,7 +159,7 @@ class ReferenceKernels:
 
     # ------------------------------------------------------------------ attention over pages
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q,
-                        seq_lens, out, scale, window, max_q_len, max_seq_len, min_q_len=1):
+                        seq_lens, out, scale, window, max_q_len, max_seq_len, min_q_len=1, weight_terms=1):
         """For request r the query tokens are rows cu_q[r] .. cu_q[r+1]-1 of qkv (their q
         heads are the first nq*d columns); the last of them stands at position
         seq_lens[r]-1.  A query at position p attends to the keys at positions
@@ -714,7 +714,7 @@ class ReferenceKernels:
             rot_pages.view(-1, rot)[slots[live]] = kr[live].to(rot_pages.dtype)
 
     def latent_attention(self, q_lat, q_rot, latent_pages, rot_pages, block_tables, cu_q, seq_lens, req_index, sink, out, scale,
-                         window, tokens, max_q_len=None, max_seq_len=None, exact=False):
+                         window, tokens, max_q_len=None, max_seq_len=None, exact=False, weight_terms=1):
         """Every head of a token attends over its request's cached latents (and the shared rotated key part)."""
         heads, seg, rank = q_lat.shape
         ps = latent_pages.shape[2]

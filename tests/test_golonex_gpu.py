@@ -215,6 +215,53 @@ def test_a_far_key_and_the_windows_edges(K, dtype, window, dist):
         assert (float((want[row] - planted_v).abs().max()) < 0.05) == inside         # the case shows what it is meant to show
 
 
+def test_softmax_weights_in_two_terms(K):
+    """Every query sees three keys, one with the largest score and two whose weight relative to it, 0.33295, lies just below
+    the middle of two bfloat16 numbers and is rounded down by 0.28 %.  With one term every output carries a bias of a tenth
+    of a percent; with two terms (the rounding and what it left out) only the output's own rounding remains, which has no
+    sign."""
+    g = gen(17)
+    n, ps = 400, 16
+    scale = 1.09976                                   # exp(-scale) = 0.33295
+    cu, seq, _, req = requests([n])
+    bt = torch.randperm(n // ps, generator=g).to(torch.int32).view(1, -1)
+    low = (torch.arange(n) % 3 != 0).float().view(n // ps, ps)                       # the keys that score lower, by position
+    low = low[torch.argsort(bt[0].long())]                                          # ... laid out by page
+    # attention over keys and values
+    H, G, d = 4, 2, 64
+    pages = torch.zeros(n // ps, 2, G, ps, d)
+    pages[:, 0, :, :, 0] = -low[:, None, :]
+    pages[:, 1] = 1.0 + torch.rand(n // ps, G, ps, d, generator=g)                  # values in (1, 2): sums keep their sign
+    pages = pages.to(torch.bfloat16)
+    q = torch.zeros(n, H, d)
+    q[:, :, 0] = 1.0
+    q = q.view(n, H * d).to(torch.bfloat16)
+    want = torch.zeros(n, H * d, dtype=torch.float64)
+    REF.paged_attention(q.double(), H, G, d, pages.double(), bt, cu, seq, want, scale, 3, n, n)
+    bias = {}
+    for terms in (1, 2):
+        got = torch.zeros(n, H * d, device="cuda", dtype=torch.bfloat16)
+        K.paged_attention(q.cuda(), H, G, d, pages.cuda(), bt.cuda(), cu.cuda(), seq.cuda(), got, scale, 3, n, n, min_q_len=n,
+                          weight_terms=terms)
+        bias[terms] = float((got.double().cpu()[2:] / want[2:] - 1.0).mean())
+    assert -1.6e-3 < bias[1] < -0.7e-3 and abs(bias[2]) < 2e-4, bias
+    # attention over latents: entry 0 of a latent is what the query reads, the others are compared
+    heads, rank = 3, 64
+    lat = 1.0 + torch.rand(n // ps, 1, ps, rank, generator=g)
+    lat[:, 0, :, 0] = -low
+    lat = lat.to(torch.bfloat16)
+    q_lat = torch.zeros(heads, n, rank)
+    q_lat[:, :, 0] = 1.0
+    want = torch.zeros(heads, n, rank, dtype=torch.float64)
+    REF.latent_attention(q_lat, None, lat.double(), None, bt, cu, seq, req, None, want, scale, 3, n)
+    for terms in (1, 2):
+        got = torch.zeros(heads, n, rank, device="cuda", dtype=torch.bfloat16)
+        K.latent_attention(q_lat.cuda(), None, lat.cuda(), None, bt.cuda(), cu.cuda(), seq.cuda(), req.cuda(), None, got, scale, 3, n,
+                           max_q_len=n, max_seq_len=n, weight_terms=terms)
+        bias[terms] = float((got.double().cpu()[:, 2:, 1:] / want[:, 2:, 1:] - 1.0).mean())
+    assert -1.6e-3 < bias[1] < -0.7e-3 and abs(bias[2]) < 2e-4, bias
+
+
 def test_queries_from_a_product_of_their_own_and_the_gate_per_head(K):
     g = gen(9)
     n, H, D, rot, dims, R, ps = 7, 3, 8, 6, 4, 16, 4
