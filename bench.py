@@ -1102,7 +1102,7 @@ def time_recurrent_kernels(args):
         bs = W // B
         xb, cw, cb = rnd(W), rnd(W, taps), rnd(W)
         ab, ib, yb, lam = rnd(W), rnd(W), rnd(W), rnd(W) - 3
-        wg = rnd(B, 2 * bs, bs, dtype=torch.bfloat16) / 8
+        wg = rnd(B, 2 * bs, 2 * bs, dtype=torch.bfloat16) / 8          # two terms of u meet the matrix repeated along k
         zb, xb2 = rnd(W), rnd(W)
         r = {}
         for label, lens in (("prompt_2048", [2048]), ("decode_8", [1] * 8)):
@@ -1115,19 +1115,19 @@ def time_recurrent_kernels(args):
             tile = K.MOE_TILE if K.moe_grouped_tc_ok(n * B, torch.bfloat16, wg) else 0
             seg = -(-n // tile) * tile if tile else n
             proj, u = rnd(n, 2 * W), torch.zeros(n, W, device="cuda")
-            ub = torch.zeros(B, seg, bs, dtype=torch.bfloat16, device="cuda")
+            ub = torch.zeros(B, seg, 2 * bs, dtype=torch.bfloat16, device="cuda")
             off = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
             tiles = torch.zeros(B * seg // tile, dtype=torch.int32, device="cuda") if tile else None
             cstate, state = torch.zeros(8, max(taps - 1, 1), W, device="cuda"), torch.zeros(8, W, device="cuda")
             gates = torch.zeros(B * seg, 2 * bs, device="cuda")
             o = torch.zeros(n, W, dtype=torch.bfloat16, device="cuda")
             r["convolution_" + label] = entry(timed(lambda: K.rglru_conv(proj, W, xb, cw, cb, cstate, slots, cu, seq, req, u, ub, off,
-                                                                         tiles, tile)), by=n * W * (4 + 4 + 2))
+                                                                         tiles, tile)), by=n * W * (4 + 4 + 4))
             if tile:
-                f = lambda: K.moe_linear_grouped(ub.view(B * seg, bs), wg, tiles, gates)      # noqa: E731
+                f = lambda: K.moe_linear_grouped(ub.view(B * seg, 2 * bs), wg, tiles, gates)      # noqa: E731
             else:
-                f = lambda: K.moe_linear(ub.view(B * seg, bs), wg, off, None, 1, gates)      # noqa: E731
-            r["gate_product_" + label] = entry(timed(f), tf=2.0 * n * B * 2 * bs * bs, by=n * W * (2 + 8) + wg.numel() * 2)
+                f = lambda: K.moe_linear(ub.view(B * seg, 2 * bs), wg, off, None, 1, gates)      # noqa: E731
+            r["gate_product_" + label] = entry(timed(f), tf=2.0 * n * B * 2 * bs * 2 * bs, by=n * W * (4 + 8) + wg.numel() * 2)
             r["recurrence_" + label] = entry(timed(lambda: K.rglru_scan(gates.view(B, seg, 2 * bs), ab, ib, lam, 8.0, u, proj, 0, yb, state,
                                                                         slots, cu, seq, o, max_q_len=max(lens))), by=n * W * 18)
             h16, cw16, o16 = rnd(n, W, dtype=torch.bfloat16), rnd(W, taps, dtype=torch.bfloat16), torch.zeros(n, W, dtype=torch.bfloat16, device="cuda")

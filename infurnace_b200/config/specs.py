@@ -553,7 +553,9 @@ class RealGatedRecurrenceSpec:
     ``conv_bias``; no activation).  u in ``blocks`` equal parts: r = sigmoid(``a_gate``[b] u_b + ``a_bias``[b]),
     i = sigmoid(``x_gate``[b] u_b + ``x_bias_gate``[b]) with square matrices [out, in] per part.
     log a = -``decay_scale`` * r * softplus(``decay``); S <- a S + sqrt(1 - a^2) * i * u per channel of a float32 state
-    that starts at zero; the output is ``o_proj``(S * y).  The convolution's last taps - 1 inputs are state too."""
+    that starts at zero; the output is ``o_proj``(S * y).  The convolution's last taps - 1 inputs are state too.
+    ``gate_terms`` 2: where the gate products' operands are bfloat16, u enters them as two terms (its rounding and what the
+    rounding left out), so that the gates see 16 bits of u instead of 8."""
     hidden_size: int
     width: int
     blocks: int
@@ -571,6 +573,7 @@ class RealGatedRecurrenceSpec:
     x_bias_gate: str
     decay: str
     o_proj: str
+    gate_terms: int = 1
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         n, W, B = self.width, self.hidden_size, self.blocks

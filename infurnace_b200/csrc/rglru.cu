@@ -4,7 +4,9 @@
 // each request's tokens in order, zeros before a sequence's start.  The K inputs before a portion come from the request's
 // state [slots, max(K, 1), width] (float32, oldest first), which then takes the portion's last K inputs.  u is written
 // twice: token-major in float32 (the recurrence reads it) and block-major [blocks, seg, width / blocks] in the products'
-// dtype (the block-diagonal gate products read it as a grouped product, a block being what an expert is there).
+// dtype (the block-diagonal gate products read it as a grouped product, a block being what an expert is there); with two
+// terms a block's row is twice as long and holds every number's rounding and then what each rounding left out, so that a
+// product against the gate matrix repeated along k sees 16 bits of every number.
 //
 // (2) rglru_scan: per channel of a float32 state, r = sigmoid(gr + a_bias), i = sigmoid(gi + i_bias) from the gate products'
 // float32 results (block-major rows of [r | i]), log a = -scale * r * softplus(lam), a = exp(log a),
@@ -46,7 +48,7 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, float* __restrict__ state,
                   const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                   const int* __restrict__ req_index, float* __restrict__ u, TB* __restrict__ ub, int seg, int blocks,
-                  int* __restrict__ offsets, int* __restrict__ tile_block, int tile, int width, int taps, int tokens, int per_block) {
+                  int* __restrict__ offsets, int* __restrict__ tile_block, int tile, int width, int taps, int tokens, int per_block, int terms) {
   ifb_pdl_wait();
   ifb_pdl_trigger();
   if (blockIdx.x == 0 && blockIdx.y == 0) {
@@ -64,13 +66,16 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
   for (int t = blockIdx.x * per_block; t < t_end; ++t) {
   const int r = req_index[t];
   const int q0 = cu_q[r], len = cu_q[r + 1] - q0, i = t - q0;
-  TB* ub_e = ub + ((size_t)(e / bs) * seg) * bs + e % bs;          // + row * bs: the V channels lie in one block (bs % V == 0)
+  // a row of a block holds bs numbers, or (terms == 2) 2 bs: every number's rounding to TB and then what each rounding left out
+  const int rowlen = terms * bs;
+  TB* ub_e = ub + ((size_t)(e / bs) * seg) * rowlen + e % bs;      // + row * rowlen: the V channels lie in one block (bs % V == 0)
   if (seq_lens[r] <= 0) {                              // a padding row of a recorded step: it stores and sees nothing
     RgVec<V> z;
 #pragma unroll
     for (int v = 0; v < V; ++v) z.v[v] = 0.f;
     rg_store<V>(u + (size_t)t * width + e, z);
-    rg_store<V>(ub_e + (size_t)t * bs, z);
+    rg_store<V>(ub_e + (size_t)t * rowlen, z);
+    if (terms == 2) rg_store<V>(ub_e + (size_t)t * rowlen + bs, z);
     continue;
   }
   const int K = taps - 1, Kp = K > 0 ? K : 1;
@@ -93,7 +98,13 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
       for (int v = 0; v < V; ++v) acc.v[v] = fmaf(__ldg(conv_w + (size_t)(e + v) * taps + j), x.v[v], acc.v[v]);
     }
     rg_store<V>(u + (size_t)(q0 + ii) * width + e, acc);
-    rg_store<V>(ub_e + (size_t)(q0 + ii) * bs, acc);
+    rg_store<V>(ub_e + (size_t)(q0 + ii) * rowlen, acc);
+    if (terms == 2) {
+      RgVec<V> rest;
+#pragma unroll
+      for (int v = 0; v < V; ++v) rest.v[v] = acc.v[v] - to_f32<TB>(from_f32<TB>(acc.v[v]));
+      rg_store<V>(ub_e + (size_t)(q0 + ii) * rowlen + bs, rest);
+    }
   };
   if (i >= K) {                                        // reads this step's rows only
     token(i);
@@ -112,8 +123,9 @@ rglru_conv_kernel(const float* __restrict__ proj, long long ld, int x_col, const
 IFB_EXPORT int ifb_rglru_conv(const float* proj, long long ld, int x_col, const float* x_bias, const float* conv_w,
                               const float* conv_b, float* state, const int* state_slots, const int* cu_q, const int* seq_lens,
                               const int* req_index, float* u, void* ub, int ub_dtype, int seg, int blocks, int* offsets,
-                              int* tile_block, int tile, int n, int width, int taps, cudaStream_t stream) {
+                              int* tile_block, int tile, int n, int width, int taps, int terms, cudaStream_t stream) {
   if (n <= 0) return IFB_OK;
+  if (terms != 1 && terms != 2) return IFB_ERR_ARG;
   if (width < 1 || blocks < 1 || width % blocks || taps < 1 || seg < n || x_col < 0 || x_col + width > ld) return IFB_ERR_SIZE;
   if (tile_block != nullptr && (tile < 1 || seg % tile)) return IFB_ERR_SIZE;
   const bool vec = (width / blocks) % 4 == 0 && ld % 4 == 0 && x_col % 4 == 0 &&
@@ -124,7 +136,7 @@ IFB_EXPORT int ifb_rglru_conv(const float* proj, long long ld, int x_col, const 
     const int per = (long long)n * ys >= 4096 ? RC_TOKENS : 1;          /* a small step keeps a block per token */                \
     return ifb_launch(rglru_conv_kernel<TB, V>, dim3((n + per - 1) / per, ys), dim3(128), 0, stream, proj, ld, x_col, x_bias,      \
                       conv_w, conv_b, state, state_slots, cu_q, seq_lens, req_index, u, (TB*)ub, seg, blocks, offsets, tile_block, \
-                      tile, width, taps, n, per);                                                                                 \
+                      tile, width, taps, n, per, terms);                                                                                 \
   }
   if (ub_dtype == IFB_BF16) { if (vec) RC_LAUNCH(__nv_bfloat16, 4); RC_LAUNCH(__nv_bfloat16, 1); }
   if (ub_dtype != IFB_F32) return IFB_ERR_DTYPE;

@@ -902,7 +902,7 @@ class CudaKernels:
             m.ifb_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
             m.ifb_rglru_conv.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                                         c_int, c_int, c_int, c_void_p]
+                                         c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_rglru_scratch_floats.restype = c_longlong
             m.ifb_rglru_scratch_floats.argtypes = [c_int, c_int, c_int]
             m.ifb_rglru_scan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
@@ -1079,13 +1079,16 @@ class CudaKernels:
         each request's tokens; the taps - 1 inputs before a portion come from state[slot] ([slots, max(taps - 1, 1), width]
         float32), which then takes the portion's last inputs.  u [n, width] float32; u_blocks [blocks, seg, width / blocks]
         in the products' dtype holds the same numbers block-major for the grouped gate products, whose segments go to
-        offsets [blocks + 1] (and tile_block [blocks * seg / tile]).  The parameters are float32."""
+        offsets [blocks + 1] (and tile_block [blocks * seg / tile]); u_blocks [blocks, seg, 2 * width / blocks] gets two
+        terms per number: the roundings, then what each rounding left out.  The parameters are float32."""
         _dense(proj, "proj", torch.float32), _dense(u, "u", torch.float32), _dense(u_blocks, "u_blocks"), _dense(state, "state", torch.float32)
         for t, name in ((x_bias, "x_bias"), (conv_weight, "conv_weight"), (conv_bias, "conv_bias")):
             _dense(t, name, torch.float32)
         _dense(offsets, "offsets", torch.int32)
         n, width = u.shape
-        blocks, seg, bs = u_blocks.shape
+        blocks, seg, rowlen = u_blocks.shape
+        terms = 2 if rowlen * blocks == 2 * width else 1
+        bs = rowlen // terms
         taps = conv_weight.shape[1]
         if blocks * bs != width or seg < n or proj.shape[0] != n or conv_weight.shape[0] != width or x_bias.numel() != width \
                 or conv_bias.numel() != width or state.shape[1:] != (max(taps - 1, 1), width) or offsets.numel() != blocks + 1:
@@ -1097,7 +1100,7 @@ class CudaKernels:
             proj.data_ptr(), proj.shape[1], int(x_col), x_bias.data_ptr(), conv_weight.data_ptr(), conv_bias.data_ptr(),
             state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), req_index.data_ptr(), u.data_ptr(),
             u_blocks.data_ptr(), _code(u_blocks), seg, blocks, offsets.data_ptr(), _ptr(tile_block), int(tile), n, width, taps,
-            self._stream()), "rglru_conv")
+            terms, self._stream()), "rglru_conv")
 
     def rglru_scan(self, gates, a_bias, i_bias, decay, decay_scale, u, proj, y_col, y_bias, state, state_slots, cu_q, seq_lens, out,
                    max_q_len=1):

@@ -27,7 +27,8 @@ MAX_POSITIONS = 1 << 20        # positions have no end in this design; block tab
 EXPERT_ACTIVATION = "silu"
 SIDE_ACTIVATION = "gelu_tanh"
 DECAY_SCALE = 8.0              # log a = -8 * r * softplus(lam)
-WEIGHT_TERMS = 2               # softmax weights are 32-bit in this design: on tensor cores they enter the sum as two bfloat16 terms
+WEIGHT_TERMS = 2               # softmax weights and the recurrence's gates are 32-bit in this design: on tensor cores they (and what
+                               # the gates read) enter their products as two bfloat16 terms
 
 
 def _rotary(rot, width):
@@ -45,7 +46,7 @@ def _mixer(kind, m, p, W, eps):
         return RealGatedRecurrenceSpec(
             hidden_size=W, width=m["width"], blocks=m["blocks"], taps=m["conv"], decay_scale=DECAY_SCALE, y_proj=p + "y",
             y_bias=p + "y.b", x_proj=p + "x", x_bias=p + "x.b", conv=p + "conv", conv_bias=p + "conv.b", a_gate=p + "ra",
-            a_bias=p + "ra.b", x_gate=p + "ri", x_bias_gate=p + "ri.b", decay=p + "lam", o_proj=p + "o")
+            a_bias=p + "ra.b", x_gate=p + "ri", x_bias_gate=p + "ri.b", decay=p + "lam", o_proj=p + "o", gate_terms=WEIGHT_TERMS)
     if kind == LATENT:
         rot_dim = int(m.get("rot_dim") or 0)
         return LatentAttentionSpec(

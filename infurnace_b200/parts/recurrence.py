@@ -171,7 +171,8 @@ class RealGatedRecurrence:
     request's tokens from the inputs its slot kept (cache entry 1) and writes u twice: float32 for the recurrence and, in the
     products' dtype, block by block for the gates.  The two block-diagonal gate matrices are one grouped product (the
     framework's grouped product with a block in an expert's place: r | i of a block are the rows of one matrix) into
-    float32.  The recurrence kernel adds the gates' biases, forms sigmoid, softplus, the decay and the input term in float32,
+    float32 (where the operands are bfloat16 and the description asks for two terms, u enters as its rounding and what the
+    rounding left out against the matrix repeated along k).  The recurrence kernel adds the gates' biases, forms sigmoid, softplus, the decay and the input term in float32,
     walks each request's tokens from the slot's state (cache entry 0; long portions in chunks side by side) and multiplies
     by the gelu branch.  A prompt, a portion and a decoded token are the same calls: the slot carries the past."""
 
@@ -186,6 +187,10 @@ class RealGatedRecurrence:
         self.y_bias, self.x_bias = f32(s.y_bias), f32(s.x_bias)
         self.conv_w, self.conv_b = f32(s.conv), f32(s.conv_bias)
         self.w_gates = torch.cat((weights[s.a_gate], weights[s.x_gate]), dim=1).contiguous()      # [blocks, 2 bs, bs]
+        # two terms of u (bfloat16 operands only): the matrix repeated along k meets [roundings | what they left out]
+        self.terms = 2 if s.gate_terms == 2 and runtime.act_dtype == torch.bfloat16 else 1
+        if self.terms == 2:
+            self.w_gates = torch.cat((self.w_gates, self.w_gates), dim=2).contiguous()           # [blocks, 2 bs, 2 bs]
         self.a_bias, self.i_bias = f32(s.a_bias).reshape(-1), f32(s.x_bias_gate).reshape(-1)
         self.decay = f32(s.decay)
         self.w_o = weights[s.o_proj]
@@ -210,16 +215,17 @@ class RealGatedRecurrence:
         seg, tile = self._segment(n)
         cap, _ = self._segment(ctx.max_rows)
         u = ctx.buffer("rg_u", (n, W), torch.float32)
-        ub = ctx.buffer("rg_u_blocks", (B * seg, bs), act, rows=B * cap).view(B, seg, bs)
+        kb = self.terms * bs
+        ub = ctx.buffer("rg_u_blocks", (B * seg, kb), act, rows=B * cap).view(B, seg, kb)
         offsets = ctx.buffer("rg_offsets", (B + 1,), torch.int32, rows=B + 1)
         tiles = ctx.buffer("rg_tiles", (B * seg // tile,), torch.int32, rows=B * cap // tile) if tile else None
         k.rglru_conv(proj, W, self.x_bias, self.conv_w, self.conv_b, ctx.state((call.cache, 1)), ctx.state_slots, ctx.cu_q,
                      ctx.seq_lens, ctx.req_index, u, ub, offsets, tiles, tile)
         gates = ctx.buffer("rg_gates", (B * seg, 2 * bs), torch.float32, rows=B * cap)
         if tile:
-            k.moe_linear_grouped(ub.view(B * seg, bs), self.w_gates, tiles, gates)
+            k.moe_linear_grouped(ub.view(B * seg, kb), self.w_gates, tiles, gates)
         else:
-            k.moe_linear(ub.view(B * seg, bs), self.w_gates, offsets, None, 1, gates)
+            k.moe_linear(ub.view(B * seg, kb), self.w_gates, offsets, None, 1, gates)
         out = ctx.buffer("rg_out", (n, W), act)
         k.rglru_scan(gates.view(B, seg, 2 * bs), self.a_bias, self.i_bias, self.decay, s.decay_scale, u, proj, 0, self.y_bias,
                      ctx.state((call.cache, 0)), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, max_q_len=ctx.max_q_len)

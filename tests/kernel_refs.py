@@ -411,7 +411,8 @@ class ReferenceKernels:
         """u_t = conv_bias + sum_j conv_weight[:, j] * xin_(t - taps + 1 + j), xin = proj[:, x_col:x_col + width] + x_bias, per
         request from the inputs its slot kept; u token-major float32 and block-major in u_blocks [blocks, seg, bs]."""
         n, width = u.shape
-        blocks, seg, bs = u_blocks.shape
+        blocks, seg, rowlen = u_blocks.shape
+        bs = width // blocks
         taps = conv_weight.shape[1]
         K = taps - 1
         xin = proj[:, x_col:x_col + width].to(self.cd) + x_bias.to(self.cd)
@@ -434,7 +435,10 @@ class ReferenceKernels:
             u[a:e] = acc.to(u.dtype)
             if K:
                 st[:K] = hist[hist.shape[0] - K:].to(st.dtype)
-        u_blocks[:, :n] = u.view(n, blocks, bs).transpose(0, 1).to(u_blocks.dtype)
+        first = u.view(n, blocks, bs).transpose(0, 1).to(u_blocks.dtype)
+        u_blocks[:, :n, :bs] = first
+        if rowlen == 2 * bs:           # two terms: the roundings, then what each rounding left out
+            u_blocks[:, :n, bs:] = (u.view(n, blocks, bs).transpose(0, 1).to(self.cd) - first.to(self.cd)).to(u_blocks.dtype)
 
     def rglru_scan(self, gates, a_bias, i_bias, decay, decay_scale, u, proj, y_col, y_bias, state, state_slots, cu_q, seq_lens, out,
                    max_q_len=1):

@@ -97,6 +97,27 @@ def test_convolution_over_steps_and_slots(K, dtype, taps, width, blocks):
         old = [a + b for a, b in zip(old, lens)]
 
 
+@pytest.mark.parametrize("width,blocks", [(320, 4), (33, 3)])
+def test_convolution_hands_the_gates_two_terms(K, width, blocks):
+    """A block's row twice as long: the bfloat16 roundings, then what each rounding left out; together 16 bits of every number."""
+    g = gen(width)
+    taps, n, bs = 3, 21, width // blocks
+    cu, seq, slots, req = requests([15, 6])
+    proj = torch.randn(n, 2 * width, generator=g) * 3
+    xb, cw, cb = torch.randn(width, generator=g), torch.randn(width, taps, generator=g), torch.randn(width, generator=g)
+    st = torch.zeros(8, taps - 1, width, device="cuda")
+    u = torch.zeros(n, width, device="cuda")
+    ub = torch.full((blocks, n + 4, 2 * bs), 9.0, device="cuda", dtype=torch.bfloat16)
+    off = torch.zeros(blocks + 1, dtype=torch.int32, device="cuda")
+    K.rglru_conv(proj.cuda(), width, xb.cuda(), cw.cuda(), cb.cuda(), st, *cuda(slots, cu, seq, req), u, ub, off)
+    want = u.view(n, blocks, bs).transpose(0, 1).double().cpu()
+    first, rest = ub[:, :n, :bs].double().cpu(), ub[:, :n, bs:].double().cpu()
+    assert torch.equal(first, want.to(torch.bfloat16).double())
+    assert float(((first + rest) - want).abs().max()) <= 2.0 ** -16 * float(want.abs().max())
+    assert float((first - want).abs().max()) > 2.0 ** -11 * float(want.abs().max())          # one term alone is far coarser
+    assert float(ub[:, n:].float().min()) == 9.0 and off.tolist() == [b * (n + 4) for b in range(blocks + 1)]
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,blocks", [(96, 3), (33, 1), (1000, 8), (260, 260)])
 def test_recurrence_in_one_launch_and_in_chunks(K, out_dtype, width, blocks):
